@@ -9,6 +9,9 @@
 // other tokens of the batch, on the page size or on which pages hold the keys.
 //
 // `sinks` (or null): a score per query head that enters the softmax's denominator and has no value.
+// `chunk` > 0: positions form chunks of that many, counted from the sequence's start, and a query reads only the keys of
+// its own chunk: lo is then at least floor(p / chunk) * chunk.  `softcap` > 0: a score s (scaled) becomes
+// softcap * tanh(s / softcap) before the softmax.
 //
 // Grid: (tokens, kv heads); a block has one warp per query head of the group, so the
 // group's warps read the same keys from shared memory.
@@ -23,7 +26,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
                                        const int* __restrict__ seq_index, const int* __restrict__ block_table,
                                        int table_stride, int page_size, T* __restrict__ out, int nq, int nkv,
                                        int hd, int window, float scale, int* __restrict__ status,
-                                       const float* __restrict__ sinks) {
+                                       const float* __restrict__ sinks, int chunk, float softcap) {
     extern __shared__ float smem[];
     const int group = nq / nkv;
     const int t = blockIdx.x, kvh = blockIdx.y;
@@ -35,7 +38,8 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
     float* Qs = Vs + KB * hd;                  // [group][hd]
     const int pos = positions[t];
     const int* table = block_table + (size_t)seq_index[t] * table_stride;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
 
     for (int d = lane; d < hd; d += 32) Qs[warp * hd + d] = to_float(q[((size_t)t * nq + head) * hd + d]) * scale;
 
@@ -72,6 +76,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
         const float* qrow = Qs + warp * hd;
         const float* krow = Ks + lane * kstride;
         for (int d = 0; d < hd; ++d) s = fmaf(qrow[d], krow[d], s);
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         s = valid ? s : -INFINITY;
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -109,13 +114,13 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
 RMX_API int rmx_attention_plain(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                                 const int* seq_index, const int* block_table, int table_stride, int page_size,
                                 void* out, int n_tokens, int nq, int nkv, int hd, int window, float scale,
-                                int* status, const float* sinks, int dtype, void* stream) {
+                                int* status, const float* sinks, int chunk, float softcap, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_plain: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
     RMX_REQUIRE(group <= 32, "attention_plain: more than 32 query heads per kv head (%d)", group);
     RMX_REQUIRE(hd > 0 && hd <= 512, "attention_plain: head_dim %d must be in 1..512", hd);
-    RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0, "attention_plain: bad page geometry");
+    RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0 && chunk >= 0, "attention_plain: bad page geometry");
     RMX_REQUIRE(nkv <= 65535, "attention_plain: too many kv heads");
     const size_t smem = ((size_t)KB * (hd + 1) + (size_t)KB * hd + (size_t)group * hd) * sizeof(float);
     RMX_REQUIRE(smem <= 200 * 1024, "attention_plain: head_dim %d with group %d needs too much shared memory", hd, group);
@@ -126,13 +131,13 @@ RMX_API int rmx_attention_plain(const void* q, const void* k_pool, const void* v
             cudaFuncSetAttribute(attention_plain_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_plain_kernel<float><<<grid, group * 32, smem, s>>>(
             (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_index, block_table, table_stride,
-            page_size, (float*)out, nq, nkv, hd, window, scale, status, sinks);
+            page_size, (float*)out, nq, nkv, hd, window, scale, status, sinks, chunk, softcap);
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(attention_plain_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_plain_kernel<__nv_bfloat16><<<grid, group * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, positions, seq_index,
-            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, window, scale, status, sinks);
+            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, window, scale, status, sinks, chunk, softcap);
     } else {
         RMX_FAIL("attention_plain: unknown dtype %d", dtype);
     }

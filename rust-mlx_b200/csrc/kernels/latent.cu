@@ -50,6 +50,70 @@ __global__ void __launch_bounds__(THREADS) latent_norms_kernel(
     for (int i = threadIdx.x; i < kv_rank; i += THREADS) dst[i] = from_float<T>(to_float(kv[i]) * inv_kv * wkv[i]);
 }
 
+// A latent with a rotated part.  One block per token.  kv = kvrow[t] holds [latent (kv_rank) | key part (rot)]:
+//   page[t] = [ kv[0 : kv_rank] / sqrt(mean(.^2) + eps) * wkv  |  rotate(kv[kv_rank : kv_rank + rot])  |  zeros up to `row` ]
+// (the key part is not normed and is shared by all heads), and of every query head h the part that is rotated,
+//   q_out[t, h, kv_rank : kv_rank + rot] = rotate(q[t, h, q_rot_at : q_rot_at + rot]),  zeros up to `row`,
+// so that a query row [its part carried into the latent's space | its rotated part] meets a page row as one dot product.
+// rotate: the pair (u, v) turns by the token's angle j into (u cos - v sin, v cos + u sin); pairs are numbers (2j, 2j + 1)
+// (`interleaved`) or (j, j + rot / 2).  cos_sin[t] = [cos of the rot / 2 angles | their sines], float.  Rotation and norm in float.
+template <typename T>
+__global__ void __launch_bounds__(THREADS) latent_rope_kernel(
+    const T* __restrict__ kvrow, int ld_kv, int kv_rank, int rot, int interleaved, const float* __restrict__ wkv, float eps,
+    const T* __restrict__ q, int ld_q, int q_head_stride, int q_rot_at, int heads, T* __restrict__ q_out, int row,
+    const float* __restrict__ cos_sin, T* __restrict__ pool, const int* __restrict__ positions, const int* __restrict__ seq_index,
+    const int* __restrict__ block_table, int table_stride, int page_size, int* __restrict__ status) {
+    __shared__ float scratch[32];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int t = blockIdx.x;
+    const int half = rot >> 1;
+    const float* cs = cos_sin + (size_t)t * rot;
+    // the queries' rotated parts
+    const int tail = row - kv_rank;          // numbers of a row after the latent's: the rotated part, then zeros
+    for (int e = threadIdx.x; e < heads * tail; e += THREADS) {
+        const int h = e / tail, d = e - h * tail;
+        float v = 0.f;
+        if (d < rot) {
+            const T* src = q + (size_t)t * ld_q + (size_t)h * q_head_stride + q_rot_at;
+            const int j = interleaved ? d >> 1 : (d < half ? d : d - half);
+            const bool first = interleaved ? (d & 1) == 0 : d < half;
+            const int other = interleaved ? d ^ 1 : (d < half ? d + half : d - half);
+            const float a = to_float(src[d]), b = to_float(src[other]);
+            v = first ? a * cs[j] - b * cs[half + j] : a * cs[j] + b * cs[half + j];
+        }
+        q_out[((size_t)t * heads + h) * row + kv_rank + d] = from_float<T>(v);
+    }
+    if (pool == nullptr) return;
+    const T* kv = kvrow + (size_t)t * ld_kv;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += THREADS) {
+        const float v = to_float(kv[i]);
+        ss += v * v;
+    }
+    const float inv_kv = rsqrtf(block_sum(ss, scratch) / (float)kv_rank + eps);
+    const int pos = positions[t];
+    const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+    if (page < 0) {
+        if (threadIdx.x == 0) atomicExch(status, 1);  // a latent was to be written to a position without a page
+        return;
+    }
+    T* dst = pool + ((size_t)page * page_size + pos % page_size) * row;
+    for (int i = threadIdx.x; i < kv_rank; i += THREADS) dst[i] = from_float<T>(to_float(kv[i]) * inv_kv * wkv[i]);
+    for (int d = threadIdx.x; d < tail; d += THREADS) {
+        float v = 0.f;
+        if (d < rot) {
+            const T* src = kv + kv_rank;
+            const int j = interleaved ? d >> 1 : (d < half ? d : d - half);
+            const bool first = interleaved ? (d & 1) == 0 : d < half;
+            const int other = interleaved ? d ^ 1 : (d < half ? d + half : d - half);
+            const float a = to_float(src[d]), b = to_float(src[other]);
+            v = first ? a * cs[j] - b * cs[half + j] : a * cs[j] + b * cs[half + j];
+        }
+        dst[kv_rank + d] = from_float<T>(v);
+    }
+}
+
 // o[t, h, :] *= sigmoid(gate[t, h]), gate rows ld_gate apart (columns of the down projection's output).
 template <typename T>
 __global__ void gate_heads_kernel(T* __restrict__ o, const T* __restrict__ gate, int ld_gate, int heads, int vdim,
@@ -110,6 +174,34 @@ RMX_API int rmx_latent_norms(const void* proj, int ld, int q_rank, int kv_rank, 
                            "latent_norms");
     else
         RMX_FAIL("latent_norms: unknown dtype %d", dtype);
+    return 0;
+}
+
+// kvrow [tokens] rows ld_kv apart: [latent (kv_rank) | key part (rot)]; q [tokens] rows ld_q apart, head h's rotated part at
+// h * q_head_stride + q_rot_at; q_out [tokens, heads, row]; pool [pages, 1, page_size, row] or null (a layer that reads another's
+// latents); cos_sin [tokens, rot].  row >= kv_rank + rot.
+RMX_API int rmx_latent_rope(const void* kvrow, int ld_kv, int kv_rank, int rot, int interleaved, const float* wkv, float eps,
+                            const void* q, int ld_q, int q_head_stride, int q_rot_at, int heads, void* q_out, int row,
+                            const float* cos_sin, void* pool, const int* positions, const int* seq_index, const int* block_table,
+                            int table_stride, int page_size, int n_tokens, int* status, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(n_tokens > 0 && kv_rank > 0 && rot >= 0 && rot % 2 == 0 && row >= kv_rank + rot && heads > 0, "latent_rope: bad sizes");
+    RMX_REQUIRE(q && q_out && (rot == 0 || cos_sin), "latent_rope: a null pointer");
+    RMX_REQUIRE(pool == nullptr || (kvrow && wkv && positions && seq_index && block_table && table_stride > 0 && page_size > 0 && status),
+                "latent_rope: writing latents needs their rows, their norm's weight, positions, the block table and a status word");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(latent_rope_kernel<float>, dim3(n_tokens), dim3(THREADS), 0, s, (const float*)kvrow, ld_kv, kv_rank,
+                                            rot, interleaved, wkv, eps, (const float*)q, ld_q, q_head_stride, q_rot_at, heads, (float*)q_out, row,
+                                            cos_sin, (float*)pool, positions, seq_index, block_table, table_stride, page_size, status),
+                           "latent_rope");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(latent_rope_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(THREADS), 0, s, (const __nv_bfloat16*)kvrow,
+                                            ld_kv, kv_rank, rot, interleaved, wkv, eps, (const __nv_bfloat16*)q, ld_q, q_head_stride, q_rot_at,
+                                            heads, (__nv_bfloat16*)q_out, row, cos_sin, (__nv_bfloat16*)pool, positions, seq_index, block_table,
+                                            table_stride, page_size, status), "latent_rope");
+    else
+        RMX_FAIL("latent_rope: unknown dtype %d", dtype);
     return 0;
 }
 

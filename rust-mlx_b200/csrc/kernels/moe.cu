@@ -142,6 +142,96 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits_in, int n_exper
     }
 }
 
+// The other way of choosing, one warp per row:
+//   s_e = sigmoid(z_e)                              what an expert's weight is made of
+//   c_e = s_e + correction_e                        what the choice goes by (correction may be null)
+//   the experts form `groups` equal groups of neighbours; a group's score is the sum of its two largest c (its one c if it
+//   has one expert); only experts of the `keep` groups with the largest scores can be chosen (the others' c counts as
+//   minus infinity: c itself may be negative)
+//   the `top` largest c among those choose the experts (ties go to the lower expert, or group)
+//   weight_e = s_e / (sum of the chosen s + 1e-20) * scale
+// Everything in float.  Shared memory: per warp n_experts floats of c, n_experts of s, `groups` of group scores.
+__global__ void moe_group_topk_kernel(const float* __restrict__ logits_in, const float* __restrict__ correction, int n_experts, int top,
+                                      int groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights, int n_rows) {
+    extern __shared__ float route_all[];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= n_rows) return;
+    float* choice = route_all + (size_t)warp * (2 * n_experts + groups);
+    float* score = choice + n_experts;
+    float* group_score = score + n_experts;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float z = logits_in[(size_t)row * n_experts + e];
+        const float sg = 1.f / (1.f + expf(-z));
+        score[e] = sg;
+        choice[e] = sg + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int per = n_experts / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;      // the largest and the second largest of the group
+            for (int i = 0; i < per; ++i) {
+                const float v = choice[g * per + i];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            group_score[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups, one after the other; a group that is kept gets +inf as its mark
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int best_g = groups;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = group_score[g];
+                if (v != INFINITY && (v > best || best_g == groups)) { best = v; best_g = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (og < groups && (best_g == groups || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+            }
+            if (lane == 0 && best_g < groups) group_score[best_g] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < n_experts; e += 32)
+            if (group_score[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
+    float mine = 0.f;      // lane k keeps the score s of the k-th chosen expert (top <= 32)
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = choice[e];
+            if (v > best) { best = v; best_e = e; }      // ascending e: the lowest index of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e >= n_experts) best_e = 0;             // (nothing left to choose from, or all values NaN: still a valid expert)
+        if (lane == k) { mine = score[best_e]; mine_id = best_e; }
+        __syncwarp();
+        if (lane == 0) choice[best_e] = -INFINITY;
+        __syncwarp();
+    }
+    // the chosen scores are added in the order in which they were chosen, by every lane alike
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) total += __shfl_sync(0xffffffffu, mine, k);
+    if (lane < top) {
+        ids[(size_t)row * top + lane] = mine_id;
+        weights[(size_t)row * top + lane] = mine / (total + 1e-20f) * scale;
+    }
+}
+
 // ---- grouping -------------------------------------------------------------------------------------------------
 // One block.  Counting sort of the pairs by expert.
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int total, int n_experts, int* __restrict__ offsets,
@@ -311,13 +401,20 @@ __global__ void moe_combine8_kernel(const __nv_bfloat16* __restrict__ y, const i
 }  // namespace
 
 // logits: [n_rows, n_experts] floats of scratch.
+// scoring 0: the `top` largest logits, weights = softmax over them.  scoring 1: sigmoid scores, chosen by score + correction among
+// the experts of the `keep` best of `groups` groups, weights = the chosen scores over their sum, times route_scale (see
+// moe_group_topk_kernel); correction may be null, groups 1 means no groups.
 RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int width, int n_experts, int top, int* ids,
-                          float* weights, float* logits, int dtype, void* stream) {
+                          float* weights, float* logits, int scoring, const float* correction, int groups, int keep,
+                          float route_scale, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(n_rows > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
                 "moe_route: %d of %d experts (at most 32 a row)", top, n_experts);
     RMX_REQUIRE(n_experts <= 2048, "moe_route: more than 2048 experts");
     RMX_REQUIRE(logits != nullptr, "moe_route: no room for the logits");
+    RMX_REQUIRE(scoring == 0 || (scoring == 1 && groups >= 1 && n_experts % groups == 0 && keep >= 1 && keep <= groups &&
+                                 (long long)keep * (n_experts / groups) >= top),
+                "moe_route: %d groups of which %d are kept do not fit %d experts of which %d are chosen", groups, keep, n_experts, top);
     cudaStream_t s = (cudaStream_t)stream;
     constexpr int ROWS = 8;
     constexpr int EXP = 1;    // (four experts a block were measured and slower: 120 us against 98 for 2,048 rows, 24 against 14 for 8)
@@ -332,8 +429,13 @@ RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int 
     else
         RMX_FAIL("moe_route: unknown dtype %d", dtype);
     const int tw = 4;
-    RMX_CHECK_LAUNCHED(launch_dependent(moe_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32), (size_t)tw * n_experts * sizeof(float), s,
-                                        (const float*)logits, n_experts, top, ids, weights, n_rows), "moe_route");
+    if (scoring == 1)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_group_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32),
+                                            (size_t)tw * (2 * n_experts + groups) * sizeof(float), s, (const float*)logits, correction, n_experts,
+                                            top, groups, keep, route_scale, ids, weights, n_rows), "moe_route");
+    else
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32), (size_t)tw * n_experts * sizeof(float), s,
+                                            (const float*)logits, n_experts, top, ids, weights, n_rows), "moe_route");
     return 0;
 }
 

@@ -19,6 +19,7 @@
 // end (tensor memory is always freed).
 #include <cuda.h>
 
+#include "activation.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -30,15 +31,8 @@ struct GroupedParams {
     const int* offsets;      // [n_experts + 1]
     int* status;
     int n_experts, N, K, ldc, k_blocks, epilogue, act;
+    float limit, alpha;      // of the gated epilogue's activation (activation.cuh), where it has such constants
 };
-
-__device__ __forceinline__ float activate(float g, int act) {
-    if (act == 1) {
-        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-        return 0.5f * g * (1.f + tanhf(inner));
-    }
-    return g / (1.f + expf(-g));
-}
 
 template <int MPAD, int STAGES, int WT>
 __global__ void __launch_bounds__(THREADS) moe_grouped_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -157,7 +151,7 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_kernel(const __grid_const
 #pragma unroll
                         for (int t = 0; t < CH; ++t)
                             if (c0 + t < rows)
-                                p.c[(size_t)(m0 + c0 + t) * p.ldc + col] = __float2bfloat16_rn(activate(acc[t], p.act) * ex[t * 64 + tid]);
+                                p.c[(size_t)(m0 + c0 + t) * p.ldc + col] = __float2bfloat16_rn(gated_act(acc[t], ex[t * 64 + tid], p.act, p.limit, p.alpha));
                     }
                 } else {
                     const int n = tile_x * TILE_N + tid;
@@ -208,14 +202,14 @@ static int g_tile_variant = 0;
 RMX_API int rmx_moe_gemm_tcgen05_supports(int N, int K) { return N >= 1 && K >= 8 && K % 8 == 0; }
 
 // A [total, K] (rows lda apart) in sorted order, W [n_experts, N, K], C [total, N] or, with epilogue 1, [total, N / 2];
-// all bfloat16.  act: 0 silu, 1 the tanh form of GELU (epilogue 1 only).
+// all bfloat16.  act, limit, alpha: the gated epilogue's activation (activation.cuh; epilogue 1 only).
 RMX_API int rmx_moe_gemm_tcgen05(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, int n_experts,
-                                 int total, int N, int K, int epilogue, int act, int* status, void* stream) {
+                                 int total, int N, int K, int epilogue, int act, float limit, float alpha, int* status, void* stream) {
     if (total == 0 || N == 0) return 0;
     RMX_REQUIRE(total > 0 && n_experts > 0 && rmx_moe_gemm_tcgen05_supports(N, K), "moe_gemm_tcgen05: bad sizes total=%d N=%d K=%d", total, N, K);
     RMX_REQUIRE(lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "moe_gemm_tcgen05: operands must be 16-byte aligned");
     RMX_REQUIRE(epilogue == 0 || (epilogue == 1 && N % 128 == 0), "moe_gemm_tcgen05: the gated epilogue needs N to be a multiple of 128, got %d", N);
-    RMX_REQUIRE(act == 0 || act == 1, "moe_gemm_tcgen05: unknown activation %d", act);
+    RMX_REQUIRE(act >= 0 && act <= 2, "moe_gemm_tcgen05: unknown activation %d", act);
     RMX_REQUIRE((long long)n_experts * N < (1ll << 31), "moe_gemm_tcgen05: too many weight rows");
     RMX_REQUIRE(offsets && status && C, "moe_gemm_tcgen05: a null pointer");
     // tiles of rows: 16 while experts have a row or two (decoding), 64, then 128
@@ -229,7 +223,7 @@ RMX_API int rmx_moe_gemm_tcgen05(const void* A, int lda, const void* W, void* C,
     if (rmx_encode_tensor_map(&ma, A, total, K, lda, mpad) != 0) return -1;
     GroupedParams p;
     p.c = (__nv_bfloat16*)C; p.offsets = offsets; p.status = status; p.n_experts = n_experts; p.N = N; p.K = K; p.ldc = ldc;
-    p.k_blocks = (K + TILE_K - 1) / TILE_K; p.epilogue = epilogue; p.act = act;
+    p.k_blocks = (K + TILE_K - 1) / TILE_K; p.epilogue = epilogue; p.act = act; p.limit = limit; p.alpha = alpha;
     dim3 grid((N + TILE_N - 1) / TILE_N, tiles_m);
     cudaStream_t s = (cudaStream_t)stream;
     if (mpad == 16) return launch_grouped<16, 6, 1>(mw, ma, p, grid, s);

@@ -5,6 +5,7 @@
 // scaling are done in float and rounded once.
 #include <type_traits>
 
+#include "activation.cuh"
 #include "common.cuh"
 
 // Four consecutive numbers as floats (the address is 16-byte aligned for float, 8 for bfloat16).
@@ -38,7 +39,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
                                  const int* __restrict__ seq_index, const int* __restrict__ slots,
                                  const int* __restrict__ last_tokens, const T* __restrict__ pos_table,
-                                 const int* __restrict__ positions, int max_positions, float scale) {
+                                 const int* __restrict__ positions, int max_positions, float scale, T* __restrict__ rows_out) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int t = blockIdx.x;
@@ -50,6 +51,9 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     const int pos = pos_table ? positions[t] : -1;
     const T* prow = (pos >= 0 && pos < max_positions) ? pos_table + (size_t)pos * width : nullptr;
     float* out = h + (size_t)t * width;
+    // rows_out (or null): the same rows once more, in the table's type, for a model whose later layers read the
+    // embedding's output again (the stream itself is overwritten as the layers add to it)
+    T* copy = rows_out ? rows_out + (size_t)t * width : nullptr;
     if ((width & 3) == 0) {  // four numbers per thread and pass
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -61,16 +65,21 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                 v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
             }
             *reinterpret_cast<float4*>(out + i) = v;
+            if (copy) store4(copy + i, v);
         }
     } else {
-        for (int i = threadIdx.x; i < width; i += blockDim.x)
-            out[i] = (ok ? to_float(row[i]) : 0.f) * scale + (prow ? to_float(prow[i]) : 0.f);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = (ok ? to_float(row[i]) : 0.f) * scale + (prow ? to_float(prow[i]) : 0.f);
+            out[i] = v;
+            if (copy) copy[i] = from_float<T>(v);
+        }
     }
 }
 
 RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
                           const int* from_last, const int* seq_index, const int* slots, const int* last_tokens,
-                          const void* pos_table, const int* positions, int max_positions, float scale, int dtype, void* stream) {
+                          const void* pos_table, const int* positions, int max_positions, float scale, void* rows_out, int dtype,
+                          void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
     RMX_REQUIRE(pos_table == nullptr || (positions && max_positions > 0), "embedding: a position table needs positions and its row count");
@@ -80,11 +89,11 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, h, width,
                                             vocab, from_last, seq_index, slots, last_tokens, (const float*)pos_table, positions,
-                                            max_positions, scale), "embedding");
+                                            max_positions, scale, (float*)rows_out), "embedding");
     else if (dtype == RMX_BF16)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids,
                                             (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index, slots, last_tokens,
-                                            (const __nv_bfloat16*)pos_table, positions, max_positions, scale), "embedding");
+                                            (const __nv_bfloat16*)pos_table, positions, max_positions, scale, (__nv_bfloat16*)rows_out), "embedding");
     else
         RMX_FAIL("embedding: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("embedding");
@@ -95,11 +104,13 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
 //   v = h[src_row] + mult * (delta[src_row] + mult2 * delta2[src_row])   (float; either delta may be null; factors of 1 change nothing)
 //   if (write_h) h[src_row] = v
 //   x[r] = v * rsqrt(mean(v^2) + eps) * w     (rounded once to T)
+//   x2[r] = v * rsqrt(mean(v^2) + eps) * w2   (w2 and x2 given: a layer with two norms of the same stream, one for each of
+//                                              two sublayers that run side by side; the mean is formed once)
 // The reduction order depends on the width and the block size only.
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult, float mult2,
                                    const int* __restrict__ rows, const float* __restrict__ w, float eps,
-                                   T* __restrict__ x, int width, int write_h) {
+                                   T* __restrict__ x, int width, int write_h, const float* __restrict__ w2, T* __restrict__ x2) {
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float vals[];
     // what follows (a product) may take its place and fetch its weights now: it waits for this kernel, and so for the
@@ -112,6 +123,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     const T* drow = delta ? delta + (size_t)src * width : nullptr;
     const T* drow2 = delta2 ? delta2 + (size_t)src * width : nullptr;
     T* xrow = x + (size_t)r * width;
+    T* xrow2 = w2 ? x2 + (size_t)r * width : nullptr;
     float ss = 0.f;
     if ((width & 3) == 0) {
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
@@ -138,6 +150,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
             const float4 v = *reinterpret_cast<const float4*>(vals + i);
             const float4 g = *reinterpret_cast<const float4*>(w + i);
             store4(xrow + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+            if (xrow2) {
+                const float4 g2 = *reinterpret_cast<const float4*>(w2 + i);
+                store4(xrow2 + i, make_float4(v.x * inv * g2.x, v.y * inv * g2.y, v.z * inv * g2.z, v.w * inv * g2.w));
+            }
         }
     } else {
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -148,7 +164,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
             ss += v * v;
         }
         const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
-        for (int i = threadIdx.x; i < width; i += blockDim.x) xrow[i] = from_float<T>(vals[i] * inv * w[i]);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            xrow[i] = from_float<T>(vals[i] * inv * w[i]);
+            if (xrow2) xrow2[i] = from_float<T>(vals[i] * inv * w2[i]);
+        }
     }
 }
 
@@ -158,7 +177,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
 template <typename T, int CHUNKS>
 __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult, float mult2,
                                         const int* __restrict__ rows, const float* __restrict__ w, float eps,
-                                        T* __restrict__ x, int width, int write_h) {
+                                        T* __restrict__ x, int width, int write_h, const float* __restrict__ w2, T* __restrict__ x2) {
     __shared__ float scratch[32];
     // the norm's weight does not come from the kernel before this one: it is fetched before the wait for it
     float4 g[CHUNKS];
@@ -211,11 +230,22 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
         if (i < width)
             store4(xrow + i, make_float4(v[c].x * inv * g[c].x, v[c].y * inv * g[c].y, v[c].z * inv * g[c].z, v[c].w * inv * g[c].w));
     }
+    if (w2) {   // the second norm of the same rows: the same mean, its own weight
+        T* xrow2 = x2 + (size_t)r * width;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int i = (c * blockDim.x + threadIdx.x) * 4;
+            if (i < width) {
+                const float4 g2 = *reinterpret_cast<const float4*>(w2 + i);
+                store4(xrow2 + i, make_float4(v[c].x * inv * g2.x, v[c].y * inv * g2.y, v[c].z * inv * g2.z, v[c].w * inv * g2.w));
+            }
+        }
+    }
 }
 
 template <typename T>
 int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, float mult2, const int* rows, const float* w, float eps, T* x,
-                       int n_rows, int width, int write_h, cudaStream_t s) {
+                       int n_rows, int width, int write_h, const float* w2, T* x2, cudaStream_t s) {
     const int groups = width / 4;
     // Which arrangement runs decides the order in which a row's squares are added.  In the 32-bit path that order
     // may depend on the width only (the same bits however a step is cut), so the number of rows chooses between
@@ -225,7 +255,7 @@ int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, fl
         // few rows (decoding): as many threads as the row has groups of four, so that a row's latency is one load
         const int threads = (groups + 31) / 32 * 32;
         RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, mult2, rows, w, eps,
-                                            x, width, write_h), "add_rmsnorm");
+                                            x, width, write_h, w2, x2), "add_rmsnorm");
         return 0;
     }
     constexpr int CHUNKS = 4;
@@ -234,49 +264,41 @@ int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, fl
         int threads = ((groups + CHUNKS - 1) / CHUNKS + 31) / 32 * 32;
         threads = threads < 32 ? 32 : threads;
         RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, mult2, rows, w, eps,
-                                            x, width, write_h), "add_rmsnorm");
+                                            x, width, write_h, w2, x2), "add_rmsnorm");
         return 0;
     }
     const int threads = block_threads(width);
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, delta2, mult, mult2, rows, w, eps, x, width,
-                                        write_h), "add_rmsnorm");
+                                        write_h, w2, x2), "add_rmsnorm");
     return 0;
 }
 
 // delta2 (or null), mult and mult2: what is added to the stream is mult * (delta + mult2 * delta2), formed in float (a layer whose
 // mixer and feed-forward read the same norm adds both at once, scaled by the model's factor).
+// w2 and x2 (or null): a second norm of the same rows with its own weight, written to x2.
 RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const void* delta2, float mult, float mult2, const int* rows, const float* w, float eps,
-                            void* x, int n_rows, int width, int write_h, int dtype, void* stream) {
+                            void* x, int n_rows, int width, int write_h, const float* w2, void* x2, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second delta without a first");
     RMX_REQUIRE(n_rows > 0 && width > 0, "add_rmsnorm: bad sizes");
     RMX_REQUIRE((size_t)width * 4 <= 160 * 1024, "add_rmsnorm: width %d is beyond 40960", width);
     RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
+    RMX_REQUIRE((w2 == nullptr) == (x2 == nullptr), "add_rmsnorm: a second weight goes with a second output");
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, (const float*)delta2, mult, mult2, rows, w, eps, (float*)x, n_rows, width, write_h, s);
+    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, (const float*)delta2, mult, mult2, rows, w, eps, (float*)x, n_rows, width, write_h, w2, (float*)x2, s);
     else if (dtype == RMX_BF16)
         rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)delta2, mult, mult2, rows, w, eps,
-                                               (__nv_bfloat16*)x, n_rows, width, write_h, s);
+                                               (__nv_bfloat16*)x, n_rows, width, write_h, w2, (__nv_bfloat16*)x2, s);
     else RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
     if (rc != 0) return rc;
     RMX_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }
 
-// out[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j], silu(z) = z / (1 + exp(-z)),
-// in float with one rounding.
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
-// The tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), times the other half of the pair.
-__device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
-    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-    return 0.5f * g * (1.f + tanhf(inner)) * u;
-}
-// act: 0 silu, 1 the tanh form of GELU
-__device__ __forceinline__ float act_mul(float g, float u, int act) { return act == 1 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
-
+// out[t, j] = act(gate_up[t, gate j], gate_up[t, up j]) (see activation.cuh), in float with one rounding.
 // Where gate j and up j lie in a row of 2 * inter numbers: concatenated [gate | up] (block == 0), or in blocks of
 // `block` gate numbers followed by their `block` up numbers.
 __device__ __forceinline__ void gate_up_at(int j, int inter, int block, int& gi, int& ui) {
@@ -290,7 +312,7 @@ __device__ __forceinline__ void gate_up_at(int j, int inter, int block, int& gi,
 }
 
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total, int act) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total, int act, float limit, float alpha) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
@@ -299,12 +321,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     gate_up_at(j, inter, block, gi, ui);
     const float g = to_float(gate_up[t * 2 * inter + gi]);
     const float u = to_float(gate_up[t * 2 * inter + ui]);
-    out[idx] = from_float<T>(act_mul(g, u, act));
+    out[idx] = from_float<T>(gated_act(g, u, act, limit, alpha));
 }
 
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
-__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4, int act) {
+__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4, int act, float limit, float alpha) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -317,22 +339,15 @@ __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ ou
     float4 g, u;
     load4(gate_up + t * 2 * inter + gi, g);
     load4(gate_up + t * 2 * inter + ui, u);
-    store4(out + t * inter + j, make_float4(act_mul(g.x, u.x, act), act_mul(g.y, u.y, act), act_mul(g.z, u.z, act), act_mul(g.w, u.w, act)));
+    store4(out + t * inter + j, make_float4(gated_act(g.x, u.x, act, limit, alpha), gated_act(g.y, u.y, act, limit, alpha), gated_act(g.z, u.z, act, limit, alpha), gated_act(g.w, u.w, act, limit, alpha)));
 }
 
 // bfloat16, sixteen outputs per thread as two groups of eight (16-byte loads and stores); inter and block are
 // multiples of 8.  blockIdx.x is the token, blockIdx.y the part of its row.  The exponential and the division are
 // the fast ones (about two units in the last place of a float): the result is rounded to bfloat16, eight bits.
-__device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
-// tanh(y) = 1 - 2 / (1 + exp(2y)), so 0.5 g (1 + tanh(y)) = g / (1 + exp(-2y)): the same fast pieces as silu
-__device__ __forceinline__ float gelu_tanh_mul_fast(float g, float u) {
-    const float y2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
-    return __fdividef(g, 1.f + __expf(-y2)) * u;
-}
-__device__ __forceinline__ float act_mul_fast(float g, float u, int act) { return act == 1 ? gelu_tanh_mul_fast(g, u) : silu_mul_fast(g, u); }
 
 __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
-                               int block, int act) {
+                               int block, int act, float limit, float alpha) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int per_row = inter >> 3;
@@ -360,18 +375,20 @@ __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_b
         for (int i = 0; i < 4; ++i) {
             const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
             const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
-            __nv_bfloat162 r = __floats2bfloat162_rn(act_mul_fast(a.x, b.x, act), act_mul_fast(a.y, b.y, act));
+            __nv_bfloat162 r = __floats2bfloat162_rn(gated_act_fast(a.x, b.x, act, limit, alpha), gated_act_fast(a.y, b.y, act, limit, alpha));
             ow[i] = *reinterpret_cast<uint32_t*>(&r);
         }
         *reinterpret_cast<uint4*>(dst + j[c]) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
-// act: which function the gate goes through before it multiplies the up half: 0 silu, 1 the tanh form of GELU.
-RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int act, int dtype, void* stream) {
+// act: which function forms an output from its gate and up numbers (activation.cuh): 0 silu, 1 the tanh form of GELU,
+// 2 the clamped swish, which reads `limit` and `alpha`.
+RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int act, float limit, float alpha, int dtype,
+                       void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
-    RMX_REQUIRE(act == 0 || act == 1, "swiglu: unknown activation %d", act);
+    RMX_REQUIRE(act >= 0 && act <= 2, "swiglu: unknown activation %d", act);
     RMX_REQUIRE(block == 0 || (block > 0 && inter % block == 0), "swiglu: blocks of %d do not divide %d", block, inter);
     const bool vec = (inter & 3) == 0 && (block & 3) == 0;
     const int threads = 256;
@@ -380,17 +397,17 @@ RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, 
         const int per_row = inter / 8;
         const int t8 = per_row >= 512 ? 256 : 128;
         RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel8, dim3(n_tokens, (per_row + 2 * t8 - 1) / (2 * t8)), dim3(t8), 0, s,
-                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, act), "swiglu");
+                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, act, limit, alpha), "swiglu");
         return 0;
     }
     const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RMX_F32) {
-        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, block, total, act), "swiglu");
-        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total, act);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, block, total, act, limit, alpha), "swiglu");
+        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total, act, limit, alpha);
     } else if (dtype == RMX_BF16) {
-        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act), "swiglu");
-        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act, limit, alpha), "swiglu");
+        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act, limit, alpha);
     } else {
         RMX_FAIL("swiglu: unknown dtype %d", dtype);
     }
@@ -448,5 +465,71 @@ RMX_API int rmx_add_bias(void* x, const float* bias, int n_rows, int width, int 
         RMX_CHECK_LAUNCHED(launch_dependent(add_bias_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (__nv_bfloat16*)x, bias, width, ld, total), "add_bias");
     else
         RMX_FAIL("add_bias: unknown dtype %d", dtype);
+    return 0;
+}
+
+// out[t] = [ round(h[t] + mult * (delta[t] + mult2 * delta2[t])) | extra[t] ]: the stream, with what the layer before left to be
+// added to it, beside `extra` rows of the same width (in T), as ONE row of 2 * width numbers in T for a product
+// that reads both (a model that mixes the embedding's output back into the stream before a group of layers).  The sum
+// is formed in float and, with write_h, stored back into the stream.
+template <typename T>
+__global__ void stream_concat_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult,
+                                     float mult2, const T* __restrict__ extra, T* __restrict__ out, int width, int write_h) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t t = blockIdx.x;
+    float* hrow = h + t * width;
+    const T* drow = delta ? delta + t * width : nullptr;
+    const T* drow2 = (delta && delta2) ? delta2 + t * width : nullptr;
+    const T* erow = extra + t * width;
+    T* orow = out + t * 2 * width;
+    if ((width & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(hrow + i);
+            if (drow) {
+                float4 d;
+                load4(drow + i, d);
+                if (drow2) {
+                    float4 e;
+                    load4(drow2 + i, e);
+                    d.x += mult2 * e.x; d.y += mult2 * e.y; d.z += mult2 * e.z; d.w += mult2 * e.w;
+                }
+                v.x += mult * d.x; v.y += mult * d.y; v.z += mult * d.z; v.w += mult * d.w;
+                if (write_h) *reinterpret_cast<float4*>(hrow + i) = v;
+            }
+            store4(orow + i, v);
+            float4 x;
+            load4(erow + i, x);
+            store4(orow + width + i, x);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = hrow[i];
+            if (drow) {
+                v += mult * (to_float(drow[i]) + (drow2 ? mult2 * to_float(drow2[i]) : 0.f));
+                if (write_h) hrow[i] = v;
+            }
+            orow[i] = from_float<T>(v);
+            orow[width + i] = erow[i];
+        }
+    }
+}
+
+RMX_API int rmx_stream_concat(float* h, const void* delta, const void* delta2, float mult, float mult2, const void* extra, void* out,
+                              int n_rows, int width, int write_h, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && width > 0 && h && extra && out, "stream_concat: bad sizes or a null pointer");
+    RMX_REQUIRE(delta != nullptr || delta2 == nullptr, "stream_concat: a second delta without a first");
+    const int threads = block_threads(width);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(stream_concat_kernel<float>, dim3(n_rows), dim3(threads), 0, s, h, (const float*)delta,
+                                            (const float*)delta2, mult, mult2, (const float*)extra, (float*)out, width, write_h), "stream_concat");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(stream_concat_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, h, (const __nv_bfloat16*)delta,
+                                            (const __nv_bfloat16*)delta2, mult, mult2, (const __nv_bfloat16*)extra, (__nv_bfloat16*)out, width,
+                                            write_h), "stream_concat");
+    else
+        RMX_FAIL("stream_concat: unknown dtype %d", dtype);
     return 0;
 }

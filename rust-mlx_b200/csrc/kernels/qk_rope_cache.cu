@@ -95,9 +95,10 @@ __global__ void __launch_bounds__(WARPS * 32) qk_rope_cache_kernel(
     }
 }
 
-// cos_sin[t][j] = cos(pos_t * inv_freq[j]), cos_sin[t][half + j] = sin(...): once per step.
+// cos_sin[t][j] = magnitude * cos(pos_t * inv_freq[j]), cos_sin[t][half + j] = magnitude * sin(...): once per step.
+// (magnitude: a factor that some scaled rotations put on the rotated numbers, and on them only; 1 otherwise.)
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ cos_sin, int n_tokens, int half) {
+                                  float* __restrict__ cos_sin, int n_tokens, int half, float magnitude) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -105,8 +106,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     const int t = idx / half, j = idx - t * half;
     float sn, cs;
     sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
-    cos_sin[(size_t)t * 2 * half + j] = cs;
-    cos_sin[(size_t)t * 2 * half + half + j] = sn;
+    cos_sin[(size_t)t * 2 * half + j] = magnitude == 1.f ? cs : cs * magnitude;
+    cos_sin[(size_t)t * 2 * half + half + j] = magnitude == 1.f ? sn : sn * magnitude;
 }
 
 // bfloat16, head size 128, all 128 numbers rotated, table given: a lane holds four neighbouring numbers of the
@@ -392,12 +393,12 @@ RMX_API int rmx_qk_whole_norm_rope_cache(const void* qkv, int row_stride, const 
 }
 
 RMX_API int rmx_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int n_tokens, int rotary_dim,
-                           void* stream) {
+                           float magnitude, void* stream) {
     if (n_tokens == 0 || rotary_dim == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table: bad sizes");
     const int half = rotary_dim / 2, total = n_tokens * half;
     RMX_CHECK_LAUNCHED(launch_dependent(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions,
-                                        inv_freq, cos_sin, n_tokens, half), "rope_table");
+                                        inv_freq, cos_sin, n_tokens, half, magnitude), "rope_table");
     return 0;
 }
 

@@ -55,13 +55,16 @@ def count_launches(n: int) -> None:
 
 
 def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, last_tokens=None, pos_table=None,
-              positions=None, scale=1.0):
+              positions=None, scale=1.0, rows_out=None):
     """h_out[t] = table[ids[t]] as float32 (the residual stream).  Where from_last[t] is set the id is the one the
     last step's sampling left for the token's sequence: last_tokens[slots[seq_index[t]]].  With ``pos_table`` the
     learned vector of the token's position, pos_table[positions[t]], is added (in float).  ``scale`` multiplies the
-    token's row (in float) before anything is added."""
+    token's row (in float) before anything is added.  ``rows_out`` ([tokens, width] of the table's dtype): the same rows once
+    more, for a model that reads the embedding's output again later."""
     lib = kernels_library()
     n, width = h_out.shape
+    if rows_out is not None and (rows_out.shape != (n, width) or rows_out.dtype != table.dtype):
+        raise KernelError("embedding: rows_out must be [tokens, width] of the table's dtype")
     if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != width):
         raise KernelError("embedding: the position table must have the token table's dtype and width")
     check(lib.rmx_embedding(_ptr(ids, torch.int32, "ids"), _ptr(table, name="table"), _ptr(h_out, torch.float32, "h"),
@@ -69,13 +72,15 @@ def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, las
                             _ptr(seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
                             _ptr(last_tokens, torch.int32, "last_tokens"), _ptr(pos_table, name="pos_table"),
                             _ptr(positions if pos_table is not None else None, torch.int32, "positions"),
-                            c_int(pos_table.shape[0] if pos_table is not None else 0), c_float(scale), c_int(dtype_code(table)), _stream()))
+                            c_int(pos_table.shape[0] if pos_table is not None else 0), c_float(scale), _ptr(rows_out, name="rows_out"),
+                            c_int(dtype_code(table)), _stream()))
     _launched()
 
 
-def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=None, mult=1.0, mult2=1.0):
+def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=None, mult=1.0, mult2=1.0, weight2=None, x2_out=None):
     """v = h + mult * (delta + mult2 * delta2); h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
-    rows rows[r] are read, x_out[r] is written and h is left alone."""
+    rows rows[r] are read, x_out[r] is written and h is left alone.  ``weight2`` and ``x2_out``: a second norm of the same
+    rows with a weight of its own (the mean of squares is formed once)."""
     lib = kernels_library()
     n = x_out.shape[0]
     width = h.shape[1]
@@ -83,11 +88,13 @@ def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=No
         raise KernelError("add_rmsnorm: delta and output must have the same dtype")
     if delta2 is not None and (delta is None or delta2.dtype != delta.dtype or delta2.shape != delta.shape):
         raise KernelError("add_rmsnorm: a second delta goes with a first of the same shape and dtype")
+    if (weight2 is None) != (x2_out is None) or (x2_out is not None and (x2_out.shape != x_out.shape or x2_out.dtype != x_out.dtype)):
+        raise KernelError("add_rmsnorm: a second weight goes with a second output like the first")
     check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(delta2, name="delta2"), c_float(mult), c_float(mult2),
                               _ptr(rows, torch.int32, "rows"),
                               _ptr(weight, torch.float32, "weight"), c_float(eps), _ptr(x_out, name="x"),
                               c_int(n), c_int(width), c_int(1 if (write_h and rows is None) else 0),
-                              c_int(dtype_code(x_out)), _stream()))
+                              _ptr(weight2, torch.float32, "weight2"), _ptr(x2_out, name="x2"), c_int(dtype_code(x_out)), _stream()))
     _launched()
 
 
@@ -108,20 +115,32 @@ def add_bias(x, bias):
     _launched()
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamp": 2}
 
 
-def swiglu(gate_up, out, block=0, activation="silu"):
-    """out = act(gate) * up, act = silu or the tanh form of GELU.  A row of ``gate_up`` is [gate | up] (block 0) or
+def activation_args(activation, args=()) -> tuple:
+    """(code, limit, alpha) of a gated feed-forward's pointwise part.  "silu" and "gelu_tanh" (out = act(gate) * up) take
+    no constants; "swish_clamp" takes ``args`` = (limit, alpha): g = min(gate, limit), u = clamp(up, -limit, limit),
+    out = g * sigmoid(alpha * g) * (u + 1)."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}: {sorted(ACTIVATIONS)}")
+    if activation == "swish_clamp":
+        if len(args) != 2 or not args[0] > 0:
+            raise KernelError("activation 'swish_clamp' takes (limit, alpha), limit positive")
+        return ACTIVATIONS[activation], float(args[0]), float(args[1])
+    return ACTIVATIONS[activation], 0.0, 0.0
+
+
+def swiglu(gate_up, out, block=0, activation="silu", args=()):
+    """out = f(gate, up) number by number, f as ``activation_args`` says.  A row of ``gate_up`` is [gate | up] (block 0) or
     blocks of ``block`` gate numbers each followed by its ``block`` up numbers."""
     lib = kernels_library()
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: gate_up must be [tokens, 2 * inter] of the output's dtype")
-    if activation not in ACTIVATIONS:
-        raise KernelError(f"swiglu: unknown activation {activation!r}: {sorted(ACTIVATIONS)}")
+    code, limit, alpha = activation_args(activation, args)
     check(lib.rmx_swiglu(_ptr(gate_up, name="gate_up"), _ptr(out, name="out"), c_int(n), c_int(inter), c_int(block),
-                         c_int(ACTIVATIONS[activation]), c_int(dtype_code(out)), _stream()))
+                         c_int(code), c_float(limit), c_float(alpha), c_int(dtype_code(out)), _stream()))
     _launched()
 
 
@@ -169,6 +188,50 @@ def latent_norms(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, pool, 
     _launched()
 
 
+def latent_rope(kv_rows, kv_rank, rot, interleaved, kv_weight, eps, q, q_rot_at, heads, q_out, row, cos_sin, pool, positions,
+                seq_index, block_table, page_size, status):
+    """A latent with a rotated part.  ``kv_rows`` [tokens, >= kv_rank + rot] (columns of wider rows allowed) are
+    [latent | key part]: the page row of a token becomes [RMSNorm(latent; kv_weight) | rotate(key part) | zeros] of ``row``
+    numbers (``pool`` [pages, 1, page_size, row], or None: nothing is written).  ``q`` [tokens, heads, size] (a view):
+    q_out[t, h, kv_rank : kv_rank + rot] = rotate(q[t, h, q_rot_at : q_rot_at + rot]), zeros behind it up to ``row``
+    (q_out [tokens, heads * row]; its first kv_rank numbers a head are not touched).  ``cos_sin`` [tokens, rot] float32:
+    cosines then sines of the token's rot / 2 angles; pairs are (2j, 2j + 1) if ``interleaved`` else (j, j + rot / 2)."""
+    lib = kernels_library()
+    n = q.shape[0]
+    if q.dim() != 3 or q.shape[1] != heads or q.stride(2) != 1 or q_out.shape != (n, heads * row) or q_out.dtype != q.dtype:
+        raise KernelError("latent_rope: q must be [tokens, heads, size] with unit stride along size, q_out [tokens, heads * row] of its dtype")
+    write = pool is not None
+    if write and (kv_rows.dim() != 2 or kv_rows.stride(1) != 1 or kv_rows.shape[1] < kv_rank + rot or kv_rows.dtype != q.dtype):
+        raise KernelError("latent_rope: kv_rows must be [tokens, >= kv_rank + rot] with unit column stride")
+    check(lib.rmx_latent_rope(
+        c_void_p(kv_rows.data_ptr() if write else 0), c_int(kv_rows.stride(0) if write else 0), c_int(kv_rank), c_int(rot),
+        c_int(1 if interleaved else 0), _ptr(kv_weight if write else None, torch.float32, "kv_weight"), c_float(eps),
+        c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(q.stride(1)), c_int(q_rot_at), c_int(heads), _ptr(q_out, name="q_out"),
+        c_int(row), _ptr(cos_sin, torch.float32, "cos_sin"), _ptr(pool if write else None, q.dtype, "pool"),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size), c_int(n),
+        _ptr(status, torch.int32, "status"), c_int(dtype_code(q)), _stream()))
+    _launched()
+
+
+def stream_concat(h, delta, extra, out, delta2=None, mult=1.0, mult2=1.0, write_h=False):
+    """out[t] = [round(h[t] + mult * (delta[t] + mult2 * delta2[t])) | extra[t]]: the stream with what is still to be added
+    to it, beside ``extra`` rows of the same width, as one row of 2 * width numbers for a product that reads both.  The
+    sum is formed in float; ``write_h`` stores it back into the stream."""
+    lib = kernels_library()
+    n, width = h.shape
+    if extra.shape != (n, width) or out.shape != (n, 2 * width) or out.dtype != extra.dtype:
+        raise KernelError("stream_concat: extra must be [tokens, width], out [tokens, 2 * width] of its dtype")
+    if delta is not None and (delta.shape != (n, width) or delta.dtype != out.dtype):
+        raise KernelError("stream_concat: delta must be [tokens, width] of the output's dtype")
+    if delta2 is not None and (delta is None or delta2.shape != delta.shape or delta2.dtype != delta.dtype):
+        raise KernelError("stream_concat: a second delta goes with a first of the same shape and dtype")
+    check(lib.rmx_stream_concat(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(delta2, name="delta2"), c_float(mult),
+                                c_float(mult2), _ptr(extra, name="extra"), _ptr(out, name="out"), c_int(n), c_int(width),
+                                c_int(1 if write_h else 0), c_int(dtype_code(out)), _stream()))
+    _launched()
+
+
 def gate_heads(o, gate, heads, vdim):
     """o[t, h, :] *= sigmoid(gate[t, h]) in place.  ``gate`` may be some columns of wider rows."""
     lib = kernels_library()
@@ -180,10 +243,14 @@ def gate_heads(o, gate, heads, vdim):
     _launched()
 
 
-def moe_route(x, w_router, top, ids_out, weights_out, logits=None):
+def moe_route(x, w_router, top, ids_out, weights_out, logits=None, scoring="softmax", correction=None, groups=1, keep=1,
+              route_scale=1.0):
     """Router of a mixture of experts: logits = x . w_router^T in float; per row the ``top`` largest choose the
     experts (ids_out [rows, top] int32), weights_out = softmax over the chosen logits.  ``logits``: [rows, experts]
-    floats of scratch (made here if not given)."""
+    floats of scratch (made here if not given).
+    ``scoring="sigmoid"``: an expert's score is sigmoid(logit); the choice goes by score + ``correction`` (float32 [experts]
+    or None) among the experts of the ``keep`` best of ``groups`` equal groups of neighbours (a group's worth: the sum of its
+    two largest corrected scores); the weights are the chosen scores over their sum, times ``route_scale``."""
     lib = kernels_library()
     n, width = x.shape
     e = w_router.shape[0]
@@ -193,9 +260,15 @@ def moe_route(x, w_router, top, ids_out, weights_out, logits=None):
         logits = torch.empty((n, e), dtype=torch.float32, device=x.device)
     elif logits.shape != (n, e):
         raise KernelError("moe_route: the logits' scratch must be [rows, experts]")
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route: unknown scoring {scoring!r}")
+    if correction is not None and correction.shape != (e,):
+        raise KernelError("moe_route: the correction must be [experts]")
     check(lib.rmx_moe_route(_ptr(x, name="x"), _ptr(w_router, torch.float32, "w_router"), c_int(n), c_int(width), c_int(e),
                             c_int(top), _ptr(ids_out, torch.int32, "ids"), _ptr(weights_out, torch.float32, "weights"),
-                            _ptr(logits, torch.float32, "logits"), c_int(dtype_code(x)), _stream()))
+                            _ptr(logits, torch.float32, "logits"), c_int(1 if scoring == "sigmoid" else 0),
+                            _ptr(correction, torch.float32, "correction"), c_int(groups), c_int(keep), c_float(route_scale),
+                            c_int(dtype_code(x)), _stream()))
     _launched(2)
 
 
@@ -244,20 +317,19 @@ def moe_gather(x, sorted_pairs, top, out):
     _launched()
 
 
-def moe_gemm_tcgen05(a, w, out, offsets, status, gated=False, activation="silu"):
+def moe_gemm_tcgen05(a, w, out, offsets, status, gated=False, activation="silu", args=()):
     """The experts' products on the tcgen05 tensor cores (bfloat16): out[p] = w[e] . a[p] for every place p of expert
     e's run; ``a`` [places, K] in sorted order, ``w`` [experts, N, K].  ``gated``: an expert's rows come in blocks of 64
-    gate rows and their 64 up rows, and out [places, N / 2] = act(gate) * up."""
+    gate rows and their 64 up rows, and out [places, N / 2] = f(gate, up) (``activation_args``)."""
     lib = kernels_library()
     e, n, k = w.shape
     total = a.shape[0]
     if a.shape[1] != k or out.shape != (total, n // 2 if gated else n) or not w.is_contiguous() or a.stride(1) != 1:
         raise KernelError(f"moe_gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
-    if activation not in ACTIVATIONS:
-        raise KernelError(f"moe_gemm_tcgen05: unknown activation {activation!r}")
+    code, limit, alpha = activation_args(activation, args)
     check(lib.rmx_moe_gemm_tcgen05(c_void_p(a.data_ptr()), c_int(a.stride(0)), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
                                    c_int(out.stride(0)), _ptr(offsets, torch.int32, "offsets"), c_int(e), c_int(total), c_int(n),
-                                   c_int(k), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]), _ptr(status, torch.int32, "status"),
+                                   c_int(k), c_int(1 if gated else 0), c_int(code), c_float(limit), c_float(alpha), _ptr(status, torch.int32, "status"),
                                    _stream()))
     _launched()
 
@@ -288,12 +360,12 @@ def gemm_plain(a, w, out):
     _launched()
 
 
-def rope_table(positions, inv_freq, rotary_dim, out):
-    """out[t] = [cos(pos_t * inv_freq[j]) for j | sin(...) for j]: the angles of a step's positions, formed once."""
+def rope_table(positions, inv_freq, rotary_dim, out, magnitude=1.0):
+    """out[t] = magnitude * [cos(pos_t * inv_freq[j]) for j | sin(...) for j]: the angles of a step's positions, formed once."""
     lib = kernels_library()
     n = positions.shape[0]
     check(lib.rmx_rope_table(_ptr(positions, torch.int32, "positions"), _ptr(inv_freq, torch.float32, "inv_freq"),
-                             _ptr(out, torch.float32, "out"), c_int(n), c_int(rotary_dim), _stream()))
+                             _ptr(out, torch.float32, "out"), c_int(n), c_int(rotary_dim), c_float(magnitude), _stream()))
     _launched()
 
 
@@ -313,8 +385,10 @@ def qk_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq
 
 
 def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_size, out, nq, nkv, hd, window,
-                    scale, status, sinks=None):
-    """``sinks`` (float32 [nq], or None): a score a query head that enters the softmax's denominator and has no value."""
+                    scale, status, sinks=None, chunk=0, softcap=0.0):
+    """``sinks`` (float32 [nq], or None): a score a query head that enters the softmax's denominator and has no value.
+    ``chunk`` > 0: a query reads only keys of its own chunk of that many positions (chunks counted from position 0).
+    ``softcap`` > 0: scaled scores go through softcap * tanh(s / softcap)."""
     lib = kernels_library()
     n = q.shape[0]
     check(lib.rmx_attention_plain(
@@ -322,7 +396,8 @@ def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_s
         _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, q.dtype, "out"), c_int(n), c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale),
-        _ptr(status, torch.int32, "status"), _ptr(sinks, torch.float32, "sinks"), c_int(dtype_code(q)), _stream()))
+        _ptr(status, torch.int32, "status"), _ptr(sinks, torch.float32, "sinks"), c_int(chunk), c_float(softcap),
+        c_int(dtype_code(q)), _stream()))
     _launched()
 
 
@@ -679,8 +754,8 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     m, k = a.shape
     n = w.shape[0]
     # swiglu: w's rows come in blocks of 64 gate rows and their 64 up rows; out is act(gate) * up, [m, n / 2]
-    if activation not in ACTIVATIONS:
-        raise KernelError(f"gemm_tcgen05: unknown activation {activation!r}")
+    if activation not in ("silu", "gelu_tanh"):
+        raise KernelError(f"gemm_tcgen05: the gated epilogue takes silu and gelu_tanh, not {activation!r}")
     want_shape = (m, n // 2) if swiglu else (m, n)
     if w.shape[1] != k or out.shape != want_shape or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} of {a.dtype}")
@@ -998,12 +1073,16 @@ class Kernels:
         return attention_flash(*args, **kwargs)
 
     def attention(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None,
-                  projection=None, sinks=None):
+                  projection=None, sinks=None, chunk=0, softcap=0.0):
         """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
         tokens with prompt portions runs as two launches, each kind with the kernel made for it.  ``projection``
         (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
-        finishes itself; ``q`` is not read."""
+        finishes itself; ``q`` is not read.  ``chunk``, ``softcap``: see ``attention_plain``."""
         group = nq // nkv
+        if chunk > 0 or softcap > 0.0:
+            attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
+                            window, scale, batch.status, sinks, chunk, softcap)
+            return
         if projection is not None:
             self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                                  projection=projection)

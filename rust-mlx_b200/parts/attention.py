@@ -123,7 +123,10 @@ class GatedAttentionMixer(Mixer):
     ``sink``: the softmax's denominator has one more term, exp(0): p_j = exp(s_j) / (1 + sum_j exp(s_j)), a key that every
         query may give weight to and that has no value;
     ``gate``: the concatenated heads are multiplied with sigmoid(W_g x), number by number, before the output product;
-    ``scale``: of the scores; ``position``: the rotation (over the first ``rotary_dim`` numbers of a head, halves paired).
+    ``scale``: of the scores; ``position``: the rotation (over the first ``rotary_dim`` numbers of a head, halves paired);
+    ``softcap`` > 0: a scaled score s becomes softcap * tanh(s / softcap) before the softmax;
+    ``chunk`` > 0: positions form chunks of that many, counted from the sequence's start, and a query at position i reads
+        key j <= i only if floor(i / chunk) = floor(j / chunk) (whatever way the prompt was cut into steps).
 
     The four products that read the layer's input (q, k, v, gate) are one product over stacked weights.
     """
@@ -133,7 +136,7 @@ class GatedAttentionMixer(Mixer):
 
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, dim: int, vdim: int, position, scale: float,
                  whole_norm_eps: float | None = None, sink: bool = False, gate: bool = False, window: int = 0,
-                 names: dict | None = None, out_name: str = "mixer_out"):
+                 names: dict | None = None, out_name: str = "mixer_out", softcap: float = 0.0, chunk: int = 0):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         self.prefix, self.width = prefix, int(width)
@@ -142,6 +145,9 @@ class GatedAttentionMixer(Mixer):
         self.position = position
         self.scale = float(scale) * float(getattr(position, "score_scale", 1.0))
         self.whole_norm_eps, self.sink, self.gate, self.window = whole_norm_eps, bool(sink), bool(gate), int(window)
+        self.softcap, self.chunk = float(softcap), int(chunk)
+        if self.softcap < 0 or self.chunk < 0:
+            raise ValueError("softcap and chunk are positive, or 0 for none")
         self.names = {k: f"{prefix}.{v}" for k, v in {**self.NAMES, **(names or {})}.items()}
         self.out_name = out_name
         self.q_norm = self.k_norm = self.sinks = None
@@ -197,7 +203,7 @@ class GatedAttentionMixer(Mixer):
             tap("q_rot", q)
         o = ws.get("attn_out", (n, nq * hd), dt)
         ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd, cache.window,
-                      self.scale, ws, sinks=self.sinks)
+                      self.scale, ws, sinks=self.sinks, chunk=self.chunk, softcap=self.softcap)
         if tap is not None:
             tap("attn_out", o)
         if self.gate:

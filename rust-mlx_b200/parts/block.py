@@ -1,7 +1,8 @@
 """How a mixer, a feed-forward and their norms are arranged in a layer.
 
 ``PreNormBlock``: h += mixer(norm1(h)); h += ffn(norm2(h)) (src/dense.rs:380-390).
-``ParallelBlock``: x = norm(h); h += factor * (mixer(x) + ffn(x)): one norm, both sublayers read it.
+``ParallelBlock``: x = norm(h); h += factor * (mixer(x) + ffn(x)): one norm, both sublayers read it; or two norms of
+the same stream, one for each sublayer.
 The residual stream is float32.  A block receives the stream together with a
 pending delta (the previous block's last output, not yet added) so that every
 add is fused with the norm that follows it; it returns the stream and its own
@@ -60,31 +61,41 @@ class PreNormBlock(Part):
 class ParallelBlock(Part):
     """One norm whose rows the mixer and the feed-forward both read; what they give is added to the stream together,
     times ``factor``: h <- h + factor * (mixer(norm(h)) + ffn(norm(h))).  ``ffn`` may be None (a layer of a mixer
-    alone).  The sum is formed in float by the norm that adds it (the next block's, or the model's last)."""
+    alone).  With ``norm2`` the feed-forward reads a norm of its own, of the same stream:
+    h <- h + factor * (mixer(norm(h)) + ffn(norm2(h))); both norms come from one kernel, which forms the rows' mean of
+    squares once.  The sum is formed in float by the norm that adds it (the next block's, or the model's last)."""
 
     graph_safe = True
 
-    def __init__(self, norm, mixer, ffn=None, factor: float = 1.0):
-        self.norm, self.mixer, self.ffn, self.factor = norm, mixer, ffn, float(factor)
+    def __init__(self, norm, mixer, ffn=None, factor: float = 1.0, norm2=None):
+        if norm2 is not None and ffn is None:
+            raise ValueError("a second norm goes with a feed-forward")
+        self.norm, self.mixer, self.ffn, self.factor, self.norm2 = norm, mixer, ffn, float(factor), norm2
 
     def children(self):
-        return [self.norm, self.mixer] + ([self.ffn] if self.ffn is not None else [])
+        return [p for p in (self.norm, self.norm2, self.mixer, self.ffn) if p is not None]
 
     def cache_specs(self):
         return self.mixer.cache_specs()
 
     def forward(self, h, pending, batch, cache):
         tap = self.ctx.tap
-        h, x = self.norm.forward(h, pending)
+        if self.norm2 is not None:
+            h, x, x_ffn = self.norm.forward(h, pending, also=self.norm2)
+        else:
+            h, x = self.norm.forward(h, pending)
+            x_ffn = x
         if tap is not None:
             tap("residual", h)
             tap("norm1", x)
+            if self.norm2 is not None:
+                tap("norm2", x_ffn)
         a = self.mixer.forward(x, batch, cache)
         if tap is not None:
             tap("mixer_out", a)
         m = None
         if self.ffn is not None:
-            m = self.ffn.forward(x, batch)
+            m = self.ffn.forward(x_ffn, batch)
             if tap is not None:
                 tap("ffn_out", m)
         return h, ScaledSum(a, m, self.factor)

@@ -14,10 +14,13 @@ from .base import ParamSpec, Part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, name: str, vocab: int, width: int, scale: float = 1.0):
+    def __init__(self, name: str, vocab: int, width: int, scale: float = 1.0, keep_rows: bool = False):
         self.name, self.vocab, self.width = name, int(vocab), int(width)
         self.scale = float(scale)   # a token's row is multiplied with this on its way into the stream (in float); a head
         self.weight = None          # tied to this table reads it unscaled
+        # the embedding's output is read again later in the step (the stream itself is overwritten as layers add to it): the
+        # kernel leaves the rows once more, in the compute dtype, as ``batch.per_step["embedding_rows"]``
+        self.keep_rows = bool(keep_rows)
 
     def param_specs(self):
         return [ParamSpec(self.name, (self.vocab, self.width), "embedding")]
@@ -30,11 +33,17 @@ class TokenEmbedding(Part):
         """Rows of the table for ``ids``; where the batch says so (``from_last``) a token's id is the one the last
         step's sampling left on the device for its sequence."""
         h = self.ctx.workspace.get("residual", (ids.shape[0], self.width), torch.float32)
+        rows = None
+        if self.keep_rows:
+            if batch is None:
+                raise ValueError("an embedding that keeps its rows for later layers needs the batch to leave them with")
+            rows = self.ctx.workspace.get("embedding_rows", (ids.shape[0], self.width), self.weight.dtype)
+            batch.per_step["embedding_rows"] = rows
         if batch is not None and batch.last_tokens is not None:
             self.ctx.ops.embedding(ids, self.weight, h, batch.from_last, batch.seq_index, batch.slots, batch.last_tokens,
-                                   scale=self.scale)
+                                   scale=self.scale, rows_out=rows)
         else:
-            self.ctx.ops.embedding(ids, self.weight, h, scale=self.scale)
+            self.ctx.ops.embedding(ids, self.weight, h, scale=self.scale, rows_out=rows)
         return h
 
 

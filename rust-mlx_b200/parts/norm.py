@@ -21,8 +21,11 @@ def _terms(delta):
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, name: str, width: int, eps: float):
+    def __init__(self, name: str, width: int, eps: float, out_scale: float = 1.0):
         self.name, self.width, self.eps = name, int(width), float(eps)
+        # what the normed rows are multiplied with besides the weight (a model that scales its logits: the factor goes
+        # through the head's product, so it may as well be put on the rows the head reads); folded into the weight, in float
+        self.out_scale = float(out_scale)
         self.weight = None
 
     def param_specs(self):
@@ -31,12 +34,23 @@ class RMSNorm(Norm):
     def bind(self, tensors, ctx):
         super().bind(tensors, ctx)
         self.weight = tensors[self.name].contiguous()
+        if self.out_scale != 1.0:
+            self.weight = (self.weight * self.out_scale).contiguous()
 
-    def forward(self, h, delta):
+    def forward(self, h, delta, also=None):
+        """``also``: a second norm of the same rows (same eps) with its own weight; the mean of squares is formed once and
+        (h, x, x of the second norm) comes back."""
         x = self.ctx.workspace.get("norm_out", (h.shape[0], self.width), self.ctx.dtype)
         first, second, factor, ratio = _terms(delta)
-        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor, mult2=ratio)
-        return h, x
+        if also is None:
+            self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor, mult2=ratio)
+            return h, x
+        if also.eps != self.eps or also.width != self.width:
+            raise ValueError("two norms of the same rows in one pass need the same eps and width")
+        x2 = self.ctx.workspace.get("norm_out_second", (h.shape[0], self.width), self.ctx.dtype)
+        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor, mult2=ratio,
+                                 weight2=also.weight, x2_out=x2)
+        return h, x, x2
 
     def forward_rows(self, h, delta, rows):
         x = self.ctx.workspace.get("norm_rows_out", (rows.shape[0], self.width), self.ctx.dtype)

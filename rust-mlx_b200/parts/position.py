@@ -17,7 +17,9 @@ definitions:
           pair index between them: the pair that makes b turns in L positions has index
           d(b) = rotary_dim * ln(L / (2 pi b)) / (2 ln theta); ramp from floor(d(beta_fast))
           to ceil(d(beta_slow)); q and k are each scaled by 0.1 ln(factor) + 1 (or
-          ``attention_factor``), so scores by its square.
+          ``attention_factor``), so scores by its square.  With ``factor_on="rotated"`` that factor
+          multiplies the cosines and sines instead, so that it reaches the rotated numbers of a head
+          only (the same thing when the whole head is rotated, not when part of it is).
 """
 from __future__ import annotations
 
@@ -49,9 +51,7 @@ def scaled_inv_freq(inv_freq: torch.Tensor, theta: float, rotary_dim: int, scali
         half = rotary_dim // 2
         low = max(math.floor(index_of(fast)), 0)
         high = min(math.ceil(index_of(slow)), rotary_dim - 1)
-        if high == low:
-            high = low + 0.001
-        ramp = ((torch.arange(half, dtype=torch.float64) - low) / (high - low)).clamp(0.0, 1.0)
+        ramp = ((torch.arange(half, dtype=torch.float64) - low) / max(high - low, 0.001)).clamp(0.0, 1.0)
         table = inv_freq / factor * ramp + inv_freq * (1.0 - ramp)
         given = scaling.get("attention_factor")
         return table, float(given) if given is not None else 0.1 * math.log(factor) + 1.0
@@ -61,8 +61,13 @@ def scaled_inv_freq(inv_freq: torch.Tensor, theta: float, rotary_dim: int, scali
 class RotaryEmbedding(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, scaling: dict | None = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, scaling: dict | None = None,
+                 factor_on: str = "scores", interleaved: bool = False):
+        if factor_on not in ("scores", "rotated"):
+            raise ValueError("factor_on is 'scores' or 'rotated'")
         self.head_dim = int(head_dim)
+        # which numbers form a pair: (j, j + rotary_dim / 2), or neighbours (2j, 2j + 1); for the kernels that ask
+        self.interleaved = bool(interleaved)
         self.rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
         self.theta = float(theta)
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
@@ -71,7 +76,9 @@ class RotaryEmbedding(PositionEncoding):
         table, qk_factor = scaled_inv_freq(self.theta ** (-2.0 * j / max(self.rotary_dim, 1)), self.theta,
                                            self.rotary_dim, scaling)
         self._table = table.to(torch.float32)
-        self.score_scale = qk_factor * qk_factor   # what the mixer multiplies its score scale with
+        # a scaled rotation's factor for q and k: on the scores (squared), or on the cosines and sines
+        self.magnitude = float(qk_factor) if factor_on == "rotated" else 1.0
+        self.score_scale = 1.0 if factor_on == "rotated" else qk_factor * qk_factor   # what the mixer multiplies its score scale with
         self.inv_freq = None
 
     def bind(self, tensors, ctx):
@@ -87,7 +94,7 @@ class RotaryEmbedding(PositionEncoding):
         key = ("rope", id(self))
         if key not in cache:
             out = self.ctx.workspace.get(f"rope_table_{id(self)}", (batch.n_tokens, self.rotary_dim), torch.float32)
-            self.ctx.ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim, out)
+            self.ctx.ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim, out, self.magnitude)
             cache[key] = out
         return cache[key]
 

@@ -12,6 +12,14 @@ device and the experts' products run over their runs of rows: in bfloat16 on the
 (``csrc/kernels/moe_tcgen05.cu``; with blocks of 64 the gate/up product forms act(gate) * up in its epilogue), in
 float32 on the FMA units with every sum in ascending k (``csrc/kernels/moe.cu``).  Nothing waits for the host, so
 decode steps can be captured in graphs.  The shared expert is a gated feed-forward like any other.
+
+Options, each a parameter:
+``scoring="sigmoid"``: an expert's score is s = sigmoid(z); the choice goes by s + correction (a tensor ``correction``, one
+    number an expert, when ``correction_name`` is given) among the experts of the ``keep_groups`` best of ``groups`` equal
+    groups of neighbouring experts (a group's worth is the sum of its two largest corrected scores; experts of other groups
+    cannot be chosen); the weights are the chosen s over their sum, times ``route_scale``.
+``activation="swish_clamp"`` with ``activation_args=(limit, alpha)``: an expert's pointwise part is
+    g = min(gate x, limit), u = clamp(up x, -limit, limit), g * sigmoid(alpha * g) * (u + 1).
 """
 from __future__ import annotations
 
@@ -25,11 +33,22 @@ class RoutedFeedForward(FeedForward):
 
     def __init__(self, prefix: str, width: int, inner: int, n_experts: int, top: int, activation: str = "silu",
                  shared: FeedForward | None = None, router_name: str = "router", expert_name: str = "e{index}",
-                 names: tuple = ("gate", "up", "down")):
+                 names: tuple = ("gate", "up", "down"), activation_args: tuple = (), scoring: str = "softmax",
+                 correction_name: str | None = None, groups: int = 1, keep_groups: int = 1, route_scale: float = 1.0):
         if not 0 < top <= n_experts:
             raise ValueError(f"a row cannot take {top} of {n_experts} experts")
         if top > 32:
             raise ValueError("at most 32 experts a row")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown scoring {scoring!r}")
+        if scoring == "softmax" and (correction_name is not None or groups != 1 or route_scale != 1.0):
+            raise ValueError("a correction, groups and a factor go with sigmoid scoring")
+        if groups < 1 or n_experts % groups or not 1 <= keep_groups <= groups or keep_groups * (n_experts // groups) < top:
+            raise ValueError(f"{groups} groups of which {keep_groups} are kept do not fit {n_experts} experts of which {top} are chosen")
+        self.activation_args = tuple(activation_args)
+        self.scoring, self.groups, self.keep_groups, self.route_scale = scoring, int(groups), int(keep_groups), float(route_scale)
+        self.correction_name = f"{prefix}.{correction_name}" if correction_name else None
+        self.correction = None
         self.prefix, self.width, self.inner = prefix, int(width), int(inner)
         self.n_experts, self.top, self.activation = int(n_experts), int(top), activation
         self.shared = shared
@@ -42,6 +61,8 @@ class RoutedFeedForward(FeedForward):
 
     def param_specs(self):
         specs = [ParamSpec(self.router, (self.n_experts, self.width), "linear", "float32")]
+        if self.correction_name:
+            specs.append(ParamSpec(self.correction_name, (self.n_experts,), "linear", "float32"))
         for gate, up, down in self.expert_names:
             specs += [ParamSpec(gate, (self.inner, self.width)), ParamSpec(up, (self.inner, self.width)),
                       ParamSpec(down, (self.width, self.inner))]
@@ -50,6 +71,8 @@ class RoutedFeedForward(FeedForward):
     def bind(self, tensors, ctx):
         super().bind(tensors, ctx)
         self.w_router = tensors[self.router].contiguous()
+        if self.correction_name:
+            self.correction = tensors[self.correction_name].contiguous()
         gu, down = [], []
         self.block = 64 if self.inner % 64 == 0 else 0
         for gate, up, d in self.expert_names:
@@ -68,7 +91,8 @@ class RoutedFeedForward(FeedForward):
         n, top, e = x.shape[0], self.top, self.n_experts
         ids = ws.get("moe_ids", (n, top), torch.int32)
         weights = ws.get("moe_weights", (n, top), torch.float32)
-        ops.moe_route(x, self.w_router, top, ids, weights, ws.get("moe_logits", (n, e), torch.float32))
+        ops.moe_route(x, self.w_router, top, ids, weights, ws.get("moe_logits", (n, e), torch.float32), scoring=self.scoring,
+                      correction=self.correction, groups=self.groups, keep=self.keep_groups, route_scale=self.route_scale)
         tap = self.ctx.tap
         if tap is not None:
             tap("moe_ids", ids)
@@ -90,13 +114,14 @@ class RoutedFeedForward(FeedForward):
             if tap is not None:
                 tap("moe_rows", rows)
             if self.block:
-                ops.moe_gemm_tcgen05(rows, self.w_gate_up, act, offsets, batch.status, gated=True, activation=self.activation)
+                ops.moe_gemm_tcgen05(rows, self.w_gate_up, act, offsets, batch.status, gated=True, activation=self.activation,
+                                     args=self.activation_args)
             else:
                 gu = ws.get("moe_gate_up", (n * top, 2 * self.inner), dt)
                 ops.moe_gemm_tcgen05(rows, self.w_gate_up, gu, offsets, batch.status)
                 if tap is not None:
                     tap("moe_gate_up", gu)
-                ops.swiglu(gu, act, 0, self.activation)
+                ops.swiglu(gu, act, 0, self.activation, self.activation_args)
             if tap is not None:
                 tap("moe_act", act)
             ops.moe_gemm_tcgen05(act, self.w_down, y, offsets, batch.status)
@@ -105,7 +130,7 @@ class RoutedFeedForward(FeedForward):
             ops.moe_gemm(x, self.w_gate_up, gu, offsets, sorted_pairs=pairs, top=top)
             if tap is not None:
                 tap("moe_gate_up", gu)
-            ops.swiglu(gu, act, self.block, self.activation)
+            ops.swiglu(gu, act, self.block, self.activation, self.activation_args)
             if tap is not None:
                 tap("moe_act", act)
             ops.moe_gemm(act, self.w_down, y, offsets)

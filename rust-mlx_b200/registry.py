@@ -75,4 +75,4 @@ def _load_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from .models import gugalorn, qwen3, resolorn  # noqa: F401  (they register themselves)
+        from .models import gugalorn, qwen3, resolorn, sosuvik  # noqa: F401  (they register themselves)
