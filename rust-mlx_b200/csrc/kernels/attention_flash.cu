@@ -68,7 +68,9 @@ struct FlashParams {
     unsigned int* counters;        // [seqs * nkv] zeros, or null: who is the last split of a (sequence, kv head)
     int* status;
     int n_seqs, n_tokens, nq, nkv, group, tq, table_stride, page_size, page_shift, window, n_splits;
+    int chunk;                     // > 0: a query reads only the keys of its own chunk of that many positions
     float scale_log2;
+    float softcap_log2, scale_over_cap;   // softcap > 0: a score s becomes softcap * tanh(s * scale / softcap), here in base-2 units
     int cluster;                   // the splits of a (sequence, kv head) are one thread-block cluster (decoding by TMA)
     // Decoding by TMA, heads of 128, one token a sequence: the kernel may take the projection's rows as they come
     // ([q heads | k heads | v heads] of every token) and, while it waits for its first keys, norm and rotate its own
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     const int* table = p.block_table + (size_t)seq * p.table_stride;
 
     // keys this tile needs: from the first row's lower bound to the last row's position
-    const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo_first = first_visible_key(pos0, p.window, p.chunk);
     const int pos_last = pos0 + n_tok - 1;
     const int kt_lo = lo_first / BN, kt_hi = pos_last / BN;
     const int n_kt = kt_hi - kt_lo + 1;
@@ -227,7 +229,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
         const int r = i == 0 ? r_lo : r_hi;
         row_ok[i] = r < rows_valid;
         row_pos[i] = pos0 + (row_ok[i] ? r / p.group : 0);
-        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+        row_lo[i] = first_visible_key(row_pos[i], p.window, p.chunk);
     }
 
     cp_async_wait<STAGES - 1>();  // Q has landed (the oldest group)
@@ -275,7 +277,7 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
                     const int i = e >> 1;
                     const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
                     const bool ok = row_ok[i] && kp <= row_pos[i] && kp >= row_lo[i];
-                    s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    s[j][e] = ok ? (p.softcap_log2 > 0.f ? p.softcap_log2 * tanh_by_exp(s[j][e] * p.scale_over_cap) : s[j][e] * p.scale_log2) : -INFINITY;
                     mx[i] = fmaxf(mx[i], s[j][e]);
                 }
             }
@@ -581,7 +583,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
     }
     const int rows_valid = n_tok * p.group;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
-    const int lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo_first = first_visible_key(pos0, p.window, p.chunk);
     const int pos_last = pos0 + n_tok - 1;
     const int kt_lo = lo_first / BN, kt_hi = pos_last / BN;
     const int per_split = (kt_hi - kt_lo + 1 + p.n_splits - 1) / p.n_splits;
@@ -685,7 +687,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         const int r = row_base + (lane >> 2) + 8 * i;
         row_ok[i] = r < rows_valid;
         row_pos[i] = pos0 + (row_ok[i] ? r / p.group : 0);
-        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+        row_lo[i] = first_visible_key(row_pos[i], p.window, p.chunk);
     }
     uint32_t qf[KSTEPS][4];
 #pragma unroll
@@ -737,7 +739,7 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
                     const int r = e >> 1;
                     const int kp = kt * BN + key_base + j * 8 + (lane & 3) * 2 + (e & 1);
                     const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
-                    s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    s[j][e] = ok ? (p.softcap_log2 > 0.f ? p.softcap_log2 * tanh_by_exp(s[j][e] * p.scale_over_cap) : s[j][e] * p.scale_log2) : -INFINITY;
                     mx[r] = fmaxf(mx[r], s[j][e]);
                 }
             }
@@ -1196,6 +1198,7 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
                                 int pool_pages, const void* qkv, int qkv_stride, const float* q_norm, const float* k_norm,
                                 float eps, const float* cos_sin, int write_kv, int first_token, int run_tokens, const float* sinks,
+                                int chunk, float softcap,
                                 int* status, void* stream) {
     if (n_tokens == 0) return 0;
     // first_token, run_tokens: the tokens of the sequences given here (a step's sequences may be given in several
@@ -1222,6 +1225,9 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;
+    p.chunk = chunk;
+    p.softcap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f;
+    p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     cudaStream_t s = (cudaStream_t)stream;
     // every tile has at most 16 rows (decoding, or very short portions): spread keys over the warps
     const bool keysplit = max_q_len > 0 && max_q_len * group <= 16;

@@ -215,6 +215,8 @@ struct Params {
     int n_seqs, nq, nkv, group, tq, table_stride, page_size, page_shift, window, box_rows;
     int per_block;   // query tiles a block takes: 2 (they share each key tile) or, for small steps, 1 (more blocks)
     float scale_log2;
+    int chunk;                     // > 0: a query reads only the keys of its own chunk of that many positions
+    float cap_over_scale, scale_over_cap;   // softcap > 0: a raw score s becomes (softcap / scale) * tanh(s * scale / softcap), still raw
     // With n_splits > 1 (a step so small that whole tiles would leave SMs without work) blockIdx.z takes one of that
     // many runs of the tile's key tiles and leaves its share, O not yet divided by the row's sum, with the row's
     // (reference maximum, sum); a second kernel adds the shares.
@@ -347,7 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
                     tma_3d(q_smem + t * Q_BYTES + x * Q_BOX, &map_q, &q_full, 64 * x, kvh * p.group, tok0 + t * p.tq);
             }
         }
-        if (p.window == 0 && p.n_splits == 1) {
+        if (p.window == 0 && p.chunk == 0 && p.n_splits == 1) {
 #pragma unroll
             for (int i = 0; i < 3; ++i) early[i] = 32 * i + lane < p.table_stride ? table[32 * i + lane] : -1;
         }
@@ -355,7 +357,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
     int n_kt = 0, kt_lo = 0, pos0 = 0, pos_last = 0, lo_first = 0;
     if (seq >= 0) {
         pos0 = p.positions[tok0];
-        lo_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+        lo_first = first_visible_key(pos0, p.window, p.chunk);
         pos_last = pos0 + n_tok - 1;
         kt_lo = lo_first / BN;
         n_kt = pos_last / BN - kt_lo + 1;
@@ -384,7 +386,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             const int e = first + lane;
             return e < p.table_stride ? table[e] : -1;
         };
-        const bool had = p.window == 0 && p.n_splits == 1;   // (then win is 0 and the entries were asked for above)
+        const bool had = p.window == 0 && p.chunk == 0 && p.n_splits == 1;   // (then win is 0 and the entries were asked for above)
         int cur = had ? early[0] : entries(win), nxt = had ? early[1] : entries(win + 32), far = had ? early[2] : entries(win + 64);
         auto wait = [&](uint64_t* bar, uint32_t parity) {
             int done = lane == 0 ? (int)mbar_wait(bar, parity) : 1;
@@ -537,7 +539,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
         const bool row_ok = r < rows_valid;
         const int tok = row_ok ? r / p.group : 0;
         const int row_pos = pos0 + t * p.tq + tok;
-        const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+        const int row_lo = first_visible_key(row_pos, p.window, p.chunk);
         const uint64_t scale2 = pair(p.scale_log2, p.scale_log2);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -552,17 +554,23 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             // registers back into tensor memory with -inf where the row must not look: such pairs are few, and the
             // code for all that follows is the same for every pair (code that a block runs once costs more to
             // fetch than to run).
+            // Scores that go through softcap * tanh(s / softcap) take the same way, pair by pair: the loop caps what
+            // the row sees (in raw units, so that all that follows stays as it is) and masks the rest.
             const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
-            if (!whole) {
+            if (!whole || p.cap_over_scale > 0.f) {
                 // key k0 + i is seen if lo <= i <= hi
                 const int lo = row_lo - k0, hi = row_ok ? min(row_pos - k0, tiles * BN - 1) : -1 << 20;
+                const bool capped = p.cap_over_scale > 0.f;
 #pragma unroll 1
                 for (int c = 0; c < 2 * BN; c += 32) {
                     uint32_t w[32];
                     tmem_ld32(s_addr + c, w);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) w[i] = (c + i >= lo && c + i <= hi) ? w[i] : 0xff800000u;   // -inf
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t seen = capped ? __float_as_uint(p.cap_over_scale * tanh_by_exp(__uint_as_float(w[i]) * p.scale_over_cap)) : w[i];
+                        w[i] = (c + i >= lo && c + i <= hi) ? seen : 0xff800000u;   // -inf
+                    }
                     tmem_st32(s_addr + c, w);
                 }
                 tmem_st_wait();
@@ -903,7 +911,8 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
                                   const int* positions, const int* block_table, int table_stride, int page_size,
                                   void* out, int n_seqs, int n_tokens, int n_tiles, int tiles_per_block, int nq, int nkv,
                                   int hd, int window, float scale, int pool_pages, int n_splits, float* part_o, float* part_ml,
-                                  int first_token, int run_tokens, const float* sinks, int* status, void* stream) {
+                                  int first_token, int run_tokens, const float* sinks, int chunk, float softcap, int* status,
+                                  void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(tiles_per_block == 1 || tiles_per_block == 2, "attention_tcgen05: a block takes 1 or 2 tiles, not %d", tiles_per_block);
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tcgen05: %d query heads over %d kv heads", nq, nkv);
@@ -925,6 +934,9 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;
+    p.chunk = chunk;
+    p.cap_over_scale = softcap > 0.f ? softcap / scale : 0.f;
+    p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     CUtensorMap mq, mk, mv;
     const long long pool_rows = (long long)pool_pages * nkv * page_size;
     if (q_map(&mq, q, n_tokens, nq, group, p.tq, hd) != 0) return -1;

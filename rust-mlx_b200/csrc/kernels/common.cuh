@@ -59,6 +59,19 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return total;
 }
 
+// What the attention kernels share of the rules for which keys a query reads and what its scores go through.
+// The first key a query at position `pos` reads (it reads up to `pos` itself): with a window, the window's first
+// position; with chunks (positions in chunks of `chunk`, counted from the sequence's start; a query reads its own chunk
+// only), the chunk's first position; the later of the two; 0 if neither.
+__device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+// tanh(x) = 1 - 2 / (exp(2x) + 1) from the fast exponential and division: an absolute error of about 1e-7 (for a score
+// that is capped by c * tanh(s / c), c times that), where tanh.approx would leave a relative 2^-11.
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.f - __fdividef(2.f, exp2f(x * 2.8853900817779268f) + 1.f); }
+
 // Programmatic dependent launch.  Every kernel here lets its dependents go first thing (before its own wait): the
 // kernel after it then takes its place and does what needs no input (a product fetches its first weight tiles) while
 // this kernel still waits for the one before, so that the prologues of up to three kernels run ahead of the data.

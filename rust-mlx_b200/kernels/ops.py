@@ -667,8 +667,14 @@ def flash_takes_projection(hd: int, group: int, page_size: int, rotary_dim: int)
     return bool(kernels_library().rmx_attention_flash_takes_projection(c_int(hd), c_int(group), c_int(page_size), c_int(rotary_dim)))
 
 
+def _key_span(max_seq_len: int, chunk: int, rows: int = 1) -> int:
+    """The most keys that ``rows`` neighbouring queries of a sequence read between them: the sequence's length, or with
+    chunks of ``chunk`` positions at most a chunk and the rows themselves."""
+    return min(max_seq_len, chunk + rows - 1) if chunk > 0 else max_seq_len
+
+
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                    n_splits=None, projection=None, use_tma=True, sinks=None):
+                    n_splits=None, projection=None, use_tma=True, sinks=None, chunk=0, softcap=0.0):
     """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike).  ``projection``:
     (qkv rows, q_norm, k_norm, eps, cos_sin, write_kv) for a decoding step whose kernel finishes the projection.
     ``use_tma``: keys and values are fetched by TMA where the kernel is built for it."""
@@ -678,7 +684,7 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
     starts = batch.q_start_host
     n_tiles = sum(-(-(starts[i + 1] - starts[i]) // tq) for i in range(batch.n_seqs))
     if n_splits is None:
-        n_splits = flash_splits(n_tiles, nkv, batch.max_seq_len)
+        n_splits = flash_splits(n_tiles, nkv, _key_span(batch.max_seq_len, chunk, tq))
     n = out.shape[0]
     qkv, q_norm, k_norm, eps, cos_sin, write_kv = projection if projection is not None else (None, None, None, 0.0, None, False)
     part_o = part_ml = counters = None
@@ -696,7 +702,7 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0),
         _ptr(qkv, torch.bfloat16, "qkv"), c_int(qkv.stride(0) if qkv is not None else 0), _ptr(q_norm, torch.float32, "q_norm"),
         _ptr(k_norm, torch.float32, "k_norm"), c_float(eps), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(1 if write_kv else 0),
-        c_int(starts[0]), c_int(starts[batch.n_seqs] - starts[0]), _ptr(sinks, torch.float32, "sinks"),
+        c_int(starts[0]), c_int(starts[batch.n_seqs] - starts[0]), _ptr(sinks, torch.float32, "sinks"), c_int(chunk), c_float(softcap),
         _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
@@ -829,7 +835,7 @@ def tcgen05_attention_shape(counts: list, nkv: int, group: int, max_seq_len: int
 
 
 def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None,
-                      n_splits=None, workspace=None, sinks=None):
+                      n_splits=None, workspace=None, sinks=None, chunk=0, softcap=0.0):
     """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory (see
     ``tcgen05_attention_shape`` for how the work is divided; ``per_block`` and ``n_splits`` override it)."""
     lib = kernels_library()
@@ -837,7 +843,7 @@ def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq,
     starts = batch.q_start_host
     counts = [starts[i + 1] - starts[i] for i in range(batch.n_seqs)]
     if per_block is None and n_splits is None:
-        per_block, n_splits = tcgen05_attention_shape(counts, nkv, nq // nkv, batch.max_seq_len)
+        per_block, n_splits = tcgen05_attention_shape(counts, nkv, nq // nkv, _key_span(batch.max_seq_len, chunk, 2 * tile))
         if workspace is None:
             n_splits = 1
     per_block = 2 if per_block is None else per_block
@@ -855,7 +861,7 @@ def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq,
         _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(per_block),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), c_int(n_splits),
         _ptr(part_o), _ptr(part_ml), c_int(starts[0]), c_int(starts[-1] - starts[0]), _ptr(sinks, torch.float32, "sinks"),
-        _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(chunk), c_float(softcap), _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -1079,10 +1085,6 @@ class Kernels:
         (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
         finishes itself; ``q`` is not read.  ``chunk``, ``softcap``: see ``attention_plain``."""
         group = nq // nkv
-        if chunk > 0 or softcap > 0.0:
-            attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                            window, scale, batch.status, sinks, chunk, softcap)
-            return
         if projection is not None:
             self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                                  projection=projection)
@@ -1092,29 +1094,31 @@ class Kernels:
             if runs is not None:
                 for run in runs:
                     self._attention_bf16(q, k_pool, v_pool, run, block_table[run.first:run.last], page_size, out, nq, nkv, hd,
-                                         window, scale, workspace, sinks)
+                                         window, scale, workspace, sinks, chunk, softcap)
                 return
-        self._attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace, sinks)
+        self._attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace, sinks,
+                             chunk, softcap)
 
     def _attention_bf16(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                        sinks=None):
+                        sinks=None, chunk=0, softcap=0.0):
         group = nq // nkv
         if (q.dtype == torch.bfloat16 and self.use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
                 and tcgen05_attention_supported(hd, group, page_size)):
             attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace,
-                              sinks=sinks)
+                              sinks=sinks, chunk=chunk, softcap=softcap)
             return
         if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
             self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                                 sinks=sinks)
+                                 sinks=sinks, chunk=chunk, softcap=softcap)
             return
         attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                        window, scale, batch.status, sinks)
+                        window, scale, batch.status, sinks, chunk, softcap)
 
-    def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype) -> int:
+    def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype, chunk: int = 0) -> int:
         """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:
         the one shape of a decode step's launches that follows the sequences' lengths."""
         # (asked once a layer and step: remembered by what the answer depends on, the length only through its key tiles)
+        max_seq_len = _key_span(max_seq_len, chunk, max(1, 64 // group))
         key = (n_seqs, nkv, hd, group, -(-max_seq_len // 64), dtype)
         found = self._splits_memo.get(key)
         if found is None:

@@ -160,7 +160,7 @@ class GatedAttentionMixer(Mixer):
 
     def graph_key(self, shape):
         return (self.ctx.ops.decode_attention_splits(shape.n_seqs, self.kv_heads, self.head_dim, self.heads // self.kv_heads,
-                                                     shape.max_seq_len, self.ctx.dtype),)
+                                                     shape.max_seq_len, self.ctx.dtype, self.chunk),)
 
     def param_specs(self):
         n, qd, kd = self.names, self.heads * self.dim, self.kv_heads * self.dim
