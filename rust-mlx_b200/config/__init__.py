@@ -2,5 +2,6 @@ from .base import ConfigError, ModelConfig, read_config_json
 from .qwen3 import Qwen3Config
 from .resolorn import ResolornConfig
 from .gugalorn import GugalornConfig
+from .sosuvik import SosuvikConfig
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "GugalornConfig", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "GugalornConfig", "SosuvikConfig", "read_config_json"]
