@@ -471,6 +471,118 @@ GUGALORN_PHASES = {"norm1": "add + norm", "norm2": "add + norm", "conv_in": "inp
                    "ffn_act": "gate/up product + activation", "ffn_out": "down product"}
 
 
+# --family sosuvik: the Sosuvik design (chunked attention with a sink and capped scores, attention through a latent with a
+# rotated key part, experts chosen among groups, a looped layer) at layer sizes of real models, beside the Resolorn design
+# (its closest relative here: latents and routed experts) and the Qwen3 dense decoder (whose attention kernels its
+# attention layers run on) of equal width, depth, heads and latent row.
+
+def sosuvik_shape(width, heads, kv_heads, dim, rot, kv_rank, rot_dim, experts, top, expert_ff, route_groups, keep, vocab, chunk, groups=1):
+    """Four layer runs a group: attention whose chunk is longer than any context here, a latent layer, (in the first
+    group the same latent layer again: a loop of two passes; elsewhere a second one), attention in chunks of ``chunk``."""
+    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": route_groups, "keep": keep}}}
+
+    def attention(size):
+        return {"type": "attention", "mlp": mlp,
+                "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                          "rot": {"base": 1e6, "dims": rot, "scaling": scaling}, "mask": {"size": size}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+                        "rot": {"base": 1e4, "dims": rot_dim}}}
+    layers = [attention(4 * MAX_CONTEXT), latent, attention(chunk)]
+    for _ in range(groups - 1):
+        layers += [attention(4 * MAX_CONTEXT), latent, latent, attention(chunk)]
+    return {"architecture": "Sosuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "loop": {"start": 1, "stop": 2, "times": 2}, "layers": layers}
+
+
+SOSUVIK_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, kv_rank=96, rot_dim=32, experts=32, top=4, expert_ff=1024, route_groups=4,
+               keep=2, vocab=32768, chunk=1024),
+    "4k": dict(width=4096, heads=16, kv_heads=4, dim=128, rot=64, kv_rank=96, rot_dim=32, experts=64, top=6, expert_ff=1408, route_groups=8,
+               keep=4, vocab=65536, chunk=1024),
+}
+
+
+def _keys_in_chunks(starts, counts, chunk):
+    """(keys the step's tokens see, keys that are read at least once): a token reads its own chunk of positions up to itself."""
+    seen = read = 0
+    for s, c in zip(starts, counts):
+        for p in range(s, s + c):
+            seen += p % chunk + 1 if chunk else p + 1
+        first = (s // chunk) * chunk if chunk else 0
+        read += s + c - first
+    return seen, read
+
+
+def sosuvik_costs(raw, starts, counts):
+    """tap name -> function(layer) -> (bytes, flops) of the kernels that end at that tap, or None where none ran."""
+    n, W = sum(counts), raw["width"]
+    everything = sum(s + c for s, c in zip(starts, counts))
+
+    def kind(att, lat=None, loop=None):
+        def cost(layer):
+            f = {"attention": att, "latent_attention": lat, "loop": loop}[layer["type"]]
+            return f(layer["mixer"]) if f is not None and layer["type"] != "loop" else (f() if f is not None else None)
+        return cost
+
+    def mlp(f):
+        return lambda layer: f(layer["mlp"]) if layer.get("mlp") else None
+
+    def touched(f):
+        e, top = f["router"]["experts"], f["router"]["top"]
+        return e * (1.0 - (1.0 - top / e) ** n)
+
+    def row(m):
+        need = m["kv_rank"] + m["rot_dim"]
+        return next((s for s in (16, 32, 64, 96, 128) if s >= need), -(-need // 16) * 16)
+
+    def chunked(m):
+        seen, read = _keys_in_chunks(starts, counts, (m.get("mask") or {}).get("size", 0))
+        return (2.0 * read * m["kv_heads"] * (m["dim"] + m["vdim"]) + 4.0 * n * m["heads"] * m["dim"],
+                2.0 * seen * m["heads"] * (m["dim"] + m["vdim"]))
+
+    return {
+        # (both norms of a layer come from one kernel: stream 4 + 4, two pending terms, two normed rows)
+        "norm1": kind(lambda m: (n * W * 16.0, 0.0), lambda m: (n * W * 16.0, 0.0)),
+        "loop_in": kind(None, None, lambda: (n * W * 14.0, 0.0)),
+        "loop_out": kind(None, None, lambda: (2.0 * (2 * W * W + 2 * n * W) + 8.0 * n * W, 4.0 * n * W * W)),
+        "qkv": kind(lambda m: _product(n, m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]), W)),
+        "q_rot": kind(lambda m: (4.0 * n * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])), 0.0)),
+        "attn_proj": kind(lambda m: _product(n, W, m["heads"] * m["vdim"])),
+        "latent_down": kind(None, lambda m: _product(n, m["heads"] * (m["dim"] + m["rot_dim"]) + m["kv_rank"] + m["rot_dim"], W)),
+        # (a product a head into the latent's space, then norm + rotation + cache write)
+        "q_latent": kind(None, lambda m: (2.0 * m["heads"] * (m["dim"] * m["kv_rank"] + n * (m["dim"] + m["kv_rank"]))
+                                          + 2.0 * n * (m["kv_rank"] + m["rot_dim"] + row(m) + 2 * m["heads"] * m["rot_dim"]),
+                                          2.0 * n * m["heads"] * m["dim"] * m["kv_rank"])),
+        "attn_out": kind(chunked, lambda m: (2.0 * everything * row(m) + 4.0 * n * m["heads"] * row(m),
+                                             4.0 * _keys_seen(starts, counts, 0) * m["heads"] * row(m))),
+        "attn_values": kind(None, lambda m: (2.0 * m["heads"] * (m["vdim"] * m["kv_rank"] + n * (m["vdim"] + m["kv_rank"])),
+                                             2.0 * n * m["heads"] * m["vdim"] * m["kv_rank"])),
+        "mixer_out": kind(None, lambda m: _product(n, W, m["heads"] * m["vdim"])),
+        "moe_ids": mlp(lambda f: (4.0 * f["router"]["experts"] * W + 2.0 * n * W, 0.0)),
+        "moe_sorted": mlp(lambda f: (12.0 * n * f["router"]["top"], 0.0)),
+        "moe_rows": mlp(lambda f: (4.0 * n * f["router"]["top"] * W, 0.0)),
+        "moe_act": mlp(lambda f: (2.0 * (touched(f) * 2 * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                  2.0 * n * f["router"]["top"] * 2 * f["expert"]["ff"] * W)),
+        "moe_expert_out": mlp(lambda f: (2.0 * (touched(f) * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                         2.0 * n * f["router"]["top"] * f["expert"]["ff"] * W)),
+        "ffn_out": mlp(lambda f: (2.0 * n * W * (f["router"]["top"] + 1), 0.0)),
+    }
+
+
+SOSUVIK_PHASES = {"norm1": "add + two norms", "loop_in": "stream beside the embedding's rows", "loop_out": "loop entry product + step vector",
+                  "qkv": "q/k/v product", "q_rot": "rotation + cache write",
+                  "attn_out": lambda layer: "attention in chunks, capped, with a sink" if layer["type"] == "attention" else "attention over latents",
+                  "attn_proj": "attention output product",
+                  "latent_down": "query and latent down product", "q_latent": "queries into the latent's space + norm + rotation + cache write",
+                  "attn_values": "values out of the latent's space (a product a head)", "mixer_out": "output product",
+                  "moe_ids": "router among groups", "moe_sorted": "grouping by expert", "moe_rows": "rows into the experts' order",
+                  "moe_act": "experts' gate/up products + clamped swish", "moe_expert_out": "experts' down products",
+                  "ffn_out": "weighted sum of the experts"}
+
+
 def _product(n, rows, cols):
     """(bytes, flops) of [n, cols] . [rows, cols]^T in bfloat16."""
     return 2.0 * (rows * cols + n * cols + n * rows), 2.0 * n * rows * cols
@@ -609,7 +721,13 @@ def phase_table(engine, seqs, costs, names, layer_of, pk, reps, warmup):
                 continue
             else:
                 label = names[name]
-            b, f = costs[name](layer_of(run))
+            layer = layer_of(run)
+            if callable(label):     # (a tap that two kinds of layer share)
+                label = label(layer)
+            cost = costs[name](layer)
+            if cost is None:
+                continue
+            b, f = cost
             key = label
             if key not in sums:
                 sums[key] = [0.0, 0, 0.0, 0.0]
@@ -635,26 +753,33 @@ def family_bench(a):
     """Decode (batch ``a.batch`` at context CONTEXT) and prefill (PREFILL_TOKENS tokens) of Resolorn layers beside Qwen3
     layers of equal width, depth, head size and feed-forward width, with every phase against its roofline."""
     import torch
-    from rust_mlx_b200.config import GugalornConfig, Qwen3Config, ResolornConfig
+    from rust_mlx_b200.config import GugalornConfig, Qwen3Config, ResolornConfig, SosuvikConfig
     from rust_mlx_b200.engine import Engine
     from rust_mlx_b200.engine.batch import SequenceInput
     pk = peaks()
-    gug = a.family == "gugalorn"
-    sizes = GUGALORN_SIZES if gug else FAMILY_SIZES
-    out = {"metric": f"{a.family.capitalize()} beside Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
+    gug, sos = a.family == "gugalorn", a.family == "sosuvik"
+    sizes = GUGALORN_SIZES if gug else SOSUVIK_SIZES if sos else FAMILY_SIZES
+    out = {"metric": f"{a.family.capitalize()} beside {'Resolorn and ' if sos else ''}Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "batch": a.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
            "peaks": pk, "sizes": {}}
     for size in (a.family_size.split(",") if a.family_size else sorted(sizes)):
         s = sizes[size]
         groups = max(1, a.family_layers // 4)
-        raw_r = gugalorn_shape(groups=groups, **s) if gug else resolorn_shape(groups=groups, **s)
+        same = FAMILY_SIZES[size] if sos else s        # (the Resolorn layers of the same name have the sizes Sosuvik lacks)
+        raw_r = gugalorn_shape(groups=groups, **s) if gug else sosuvik_shape(groups=groups, **s) if sos else resolorn_shape(groups=groups, **s)
         raw_q = dict(QWEN3_8B, num_hidden_layers=4 * groups, hidden_size=s["width"], num_attention_heads=s["heads"],
-                     num_key_value_heads=s["kv_heads"] if gug else max(1, s["heads"] // 4), head_dim=s["dim"],
-                     intermediate_size=s["ff"], vocab_size=s["vocab"], max_position_embeddings=2 * MAX_CONTEXT)
+                     num_key_value_heads=s["kv_heads"] if gug or sos else max(1, s["heads"] // 4), head_dim=s["dim"],
+                     intermediate_size=same["ff"], vocab_size=s["vocab"], max_position_embeddings=2 * MAX_CONTEXT)
         result = {}
         mine = ("gugalorn", raw_r, GugalornConfig.from_dict(raw_r), gugalorn_costs, GUGALORN_PHASES) if gug else \
+               ("sosuvik", raw_r, SosuvikConfig.from_dict(raw_r), sosuvik_costs, SOSUVIK_PHASES) if sos else \
                ("resolorn", raw_r, ResolornConfig.from_dict(raw_r), resolorn_costs, RESOLORN_PHASES)
-        for family, raw, cfg, costs_of, names in (mine, ("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES)):
+        others = []
+        if sos:
+            raw_o = resolorn_shape(groups=groups, **same)
+            others.append(("resolorn", raw_o, ResolornConfig.from_dict(raw_o), resolorn_costs, RESOLORN_PHASES))
+        others.append(("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES))
+        for family, raw, cfg, costs_of, names in (mine, *others):
             cache_tokens = a.batch * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64) + 2 * PREFILL_TOKENS
             engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
                             max_requests=a.batch + 4, tuning=a.policy)
@@ -664,7 +789,11 @@ def family_bench(a):
                     grp.v_pool.normal_(0, 1)
             ms, launches, clock_info = time_decode(engine, a.batch, a.steps, a.warmup, ClockSampler())
             pf_ms = time_prefill(engine, PREFILL_TOKENS)
-            layer_of = (lambda run, raw=raw: raw["layers"][run]) if family != "qwen3" else (lambda run: {})
+            if family == "qwen3":
+                layer_of = lambda run: {}
+            else:       # a run of the schedule is a layer, or (past the layers) a loop's entry
+                layer_of = lambda run, raw=raw, calls=engine._calls: (raw["layers"][calls[run][0].layer]
+                                                                      if calls[run][0].layer < len(raw["layers"]) else {"type": "loop"})
             # phases of a decode step and of a prompt
             run = DecodeRun(engine, a.batch, CONTEXT)
             try:
@@ -724,7 +853,7 @@ def main():
     ap.add_argument("--continuous", action="store_true",
                     help="instead: 64 requests with prompts of 128..3072 random ids, 256 tokens each, through the "
                          "scheduler with chunked prefill of 512 (continuous batching); prints its own JSON line")
-    ap.add_argument("--family", default="", choices=["", "resolorn", "gugalorn"],
+    ap.add_argument("--family", default="", choices=["", "resolorn", "gugalorn", "sosuvik"],
                     help="instead: layers of this design at sizes of real models beside Qwen3 layers of equal width, depth, head "
                          "size and feed-forward width: decode and prefill tok/s and every phase against its roofline; prints its own "
                          "JSON line")

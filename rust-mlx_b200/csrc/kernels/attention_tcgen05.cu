@@ -707,9 +707,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             fence_after();
             const int g = r - tok * p.group;
             const size_t row = (size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g;
-            // a sink: one more term in the row's sum, relative to the same reference as the others, in the first run's share
+            // a sink: one more term in the row's sum, relative to the same reference as the others.  When the keys are
+            // split into runs the merge adds it: with chunks a row may see no key of a run, the first one included
             // (a sum that overflows to infinity gives the zeros that it should)
-            if (p.sinks != nullptr && row_ok && blockIdx.z == 0 && n_kt > 0) l += exp2f(p.sinks[kvh * p.group + g] * LOG2E - m);   // (a row past the tile's last has no head)
+            if (p.sinks != nullptr && row_ok && p.n_splits == 1 && n_kt > 0) l += exp2f(p.sinks[kvh * p.group + g] * LOG2E - m);   // (a row past the tile's last has no head)
             if (p.n_splits > 1) {
                 // this run's share of the row (a run without keys leaves maximum -inf and sum 0, and no numbers)
                 float* dst = p.part_o + ((size_t)blockIdx.z * p.n_rows + row) * HD;
@@ -764,7 +765,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
 template <int HD>
 __global__ void __launch_bounds__(128) attention_tcgen05_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                       __nv_bfloat16* __restrict__ out, int n_rows, int n_splits,
-                                                                      int first_row, int rows) {
+                                                                      int first_row, int rows, const float* __restrict__ sinks, int nq) {
     constexpr int PER = HD / 32;
     const int lane = threadIdx.x & 31;
     if (blockIdx.x * 4 + (threadIdx.x >> 5) >= rows) return;
@@ -788,6 +789,7 @@ __global__ void __launch_bounds__(128) attention_tcgen05_merge_kernel(const floa
             acc[i + 1] += f * v.y;
         }
     }
+    if (sinks != nullptr) L += exp2f(sinks[row % nq] * LOG2E - M);   // the sink's term, once a row (rows are [token, head])
     const float inv = L > 0.f ? 1.f / L : 0.f;
     __nv_bfloat16* dst = out + (size_t)row * HD + lane * PER;
 #pragma unroll
@@ -885,7 +887,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     RMX_CHECK_LAUNCH("attention_tcgen05");
     if (p.n_splits > 1) {
         attention_tcgen05_merge_kernel<HD><<<(run_tokens * p.nq + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, p.n_rows, p.n_splits,
-                                                                                          first_token * p.nq, run_tokens * p.nq);
+                                                                                          first_token * p.nq, run_tokens * p.nq, p.sinks, p.nq);
         RMX_CHECK_LAUNCH("attention_tcgen05_merge");
     }
     return 0;

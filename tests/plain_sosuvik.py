@@ -142,14 +142,40 @@ def choose_experts(z, correction, router):
     return ids, chosen / (chosen.sum(-1, keepdim=True) + 1e-20) * router.get("scale", 1.0)
 
 
+def choice_margin(z, correction, router):
+    """[T]: how far a row's choice is from another one: the smallest of the gap between the last chosen and the first
+    unchosen corrected score (among the kept groups) and the gap between the last kept and the first dropped group's worth.
+    Infinite where there is nothing to choose.  (A test in reduced precision leaves rows with a small margin out.)"""
+    E, top = router["experts"], router["top"]
+    c = torch.sigmoid(z) + correction
+    margin = torch.full((z.shape[0],), math.inf, dtype=z.dtype)
+    groups = router.get("groups")
+    if groups and groups["count"] > 1:
+        n, keep = groups["count"], groups["keep"]
+        per = E // n
+        worth = c.view(-1, n, per).topk(min(2, per), dim=-1).values.sum(-1)
+        ranked = worth.sort(-1, descending=True)
+        if keep < n:
+            margin = ranked.values[:, keep - 1] - ranked.values[:, keep]
+        kept = torch.zeros_like(worth, dtype=torch.bool).scatter_(1, ranked.indices[:, :keep], True)
+        c = c.masked_fill(~kept.repeat_interleave(per, dim=1), -math.inf)
+    ranked = c.sort(-1, descending=True).values
+    if top < E:
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])     # (infinite when the next one is out)
+    return margin
+
+
 def clamped_expert(x, gate, up, down, limit, bf16=False):
     g = rnd(x @ gate.T, bf16).clamp(max=limit)
     u = rnd(x @ up.T, bf16).clamp(-limit, limit)
     return rnd(rnd(g * torch.sigmoid(1.702 * g) * (u + 1.0), bf16) @ down.T, bf16)
 
 
-def grouped_experts(x, w, prefix, mlp, bf16=False):
-    ids, weights = choose_experts(x @ w[f"{prefix}.router"].T, w[f"{prefix}.correction"], mlp["router"])
+def grouped_experts(x, w, prefix, mlp, bf16=False, margins_out=None):
+    z = x @ w[f"{prefix}.router"].T
+    ids, weights = choose_experts(z, w[f"{prefix}.correction"], mlp["router"])
+    if margins_out is not None:
+        margins_out.append(choice_margin(z, w[f"{prefix}.correction"], mlp["router"]))
     out = torch.zeros_like(x)
     for e in range(mlp["router"]["experts"]):
         rows, slot = torch.nonzero(ids == e, as_tuple=True)
@@ -175,8 +201,9 @@ def order_of_runs(config):
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(config, w, tokens, bf16=False, layers_out=None):
-    """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the stream after every layer run."""
+def forward(config, w, tokens, bf16=False, layers_out=None, margins_out=None):
+    """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the stream after every layer run;
+    ``margins_out``: one that receives every routed layer run's ``choice_margin``."""
     eps = config["norm"]["eps"]
     x0 = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     x = x0.clone()
@@ -193,7 +220,7 @@ def forward(config, w, tokens, bf16=False, layers_out=None):
             raise ValueError(layer["type"])
         if layer.get("mlp"):
             h2 = rnd(rms_norm(x, w[f"{p}.norm2"], eps), bf16)
-            total = total + grouped_experts(h2, w, f"{p}.mlp", layer["mlp"], bf16)
+            total = total + grouped_experts(h2, w, f"{p}.mlp", layer["mlp"], bf16, margins_out)
         x = x + total
         if layers_out is not None:
             layers_out.append(x.clone())
