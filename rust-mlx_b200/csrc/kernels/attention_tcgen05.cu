@@ -173,10 +173,16 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-// 2^x on the special-function unit (x <= 0 here; -inf gives 0).
+// 2^x on the special-function unit (-inf gives 0, large x gives inf).
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// 1 / x on the special-function unit (1 / inf = 0).
+__device__ __forceinline__ float rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
 // Two floats in one 64-bit register, for the instructions that work on such pairs, and the maximum of three.
@@ -195,6 +201,29 @@ __device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
     uint64_t r;
     asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
     return r;
+}
+__device__ __forceinline__ uint64_t mul_pair(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// c tanh(x) = c - 2c / (2^(2 x log2 e) + 1) of four raw scores at once; k = 2 log2 e / c' and c, -2c as pairs (c' in the
+// units of the scaled score, c in raw units).  The exponent is held at 30 (2^30 + 1 and 2^30 are the same float, so
+// nothing is lost); the four divisors, each between 1 and 2^30, then share ONE reciprocal: 1 / (d0 d1 d2 d3) times the
+// other three.  The special-function unit, which bounds this kernel, is asked for five results instead of eight;
+// the products run on pairs of floats.  The absolute error of tanh stays below 1e-6.
+__device__ __forceinline__ void cap4(float& s0, float& s1, float& s2, float& s3, uint64_t k, uint64_t c, uint64_t m2c) {
+    float t0, t1, t2, t3;
+    unpair(mul_pair(pair(s0, s2), k), t0, t2);
+    unpair(mul_pair(pair(s1, s3), k), t1, t3);
+    const uint64_t d02 = add_pair(pair(ex2(fminf(t0, 30.f)), ex2(fminf(t2, 30.f))), pair(1.f, 1.f));
+    const uint64_t d13 = add_pair(pair(ex2(fminf(t1, 30.f)), ex2(fminf(t3, 30.f))), pair(1.f, 1.f));
+    float p01, p23;
+    unpair(mul_pair(d02, d13), p01, p23);                     // d0 d1, d2 d3
+    const float r = rcp(p01 * p23);
+    const uint64_t r0123 = mul_pair(pair(r, r), pair(p23, p01));   // 1 / (d0 d1), 1 / (d2 d3)
+    unpair(fma_pair(mul_pair(r0123, d13), m2c, c), s0, s2);   // 1 / d0 = d1 / (d0 d1), 1 / d2 = d3 / (d2 d3)
+    unpair(fma_pair(mul_pair(r0123, d02), m2c, c), s1, s3);
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
@@ -554,22 +583,28 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             // registers back into tensor memory with -inf where the row must not look: such pairs are few, and the
             // code for all that follows is the same for every pair (code that a block runs once costs more to
             // fetch than to run).
-            // Scores that go through softcap * tanh(s / softcap) take the same way, pair by pair: the loop caps what
-            // the row sees (in raw units, so that all that follows stays as it is) and masks the rest.
+            // Scores that go through softcap * tanh(s / softcap) are capped in raw units, so that all that follows stays
+            // as it is: in that loop for a pair that is masked anyway, in registers after the load (below) for a whole one.
             const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
-            if (!whole || p.cap_over_scale > 0.f) {
+            const bool capped = p.cap_over_scale > 0.f;
+            if (!whole) {
                 // key k0 + i is seen if lo <= i <= hi
                 const int lo = row_lo - k0, hi = row_ok ? min(row_pos - k0, tiles * BN - 1) : -1 << 20;
-                const bool capped = p.cap_over_scale > 0.f;
+                const uint64_t cap_in = pair(p.scale_over_cap * (2.f * LOG2E), p.scale_over_cap * (2.f * LOG2E));
+                const uint64_t cap_c = pair(p.cap_over_scale, p.cap_over_scale), cap_m2 = pair(-2.f * p.cap_over_scale, -2.f * p.cap_over_scale);
 #pragma unroll 1
                 for (int c = 0; c < 2 * BN; c += 32) {
                     uint32_t w[32];
                     tmem_ld32(s_addr + c, w);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t seen = capped ? __float_as_uint(p.cap_over_scale * tanh_by_exp(__uint_as_float(w[i]) * p.scale_over_cap)) : w[i];
-                        w[i] = (c + i >= lo && c + i <= hi) ? seen : 0xff800000u;   // -inf
+                    for (int i = 0; i < 32; i += 4) {
+                        float s0 = __uint_as_float(w[i]), s1 = __uint_as_float(w[i + 1]), s2 = __uint_as_float(w[i + 2]), s3 = __uint_as_float(w[i + 3]);
+                        if (capped) cap4(s0, s1, s2, s3, cap_in, cap_c, cap_m2);
+                        w[i] = (c + i >= lo && c + i <= hi) ? __float_as_uint(s0) : 0xff800000u;   // -inf
+                        w[i + 1] = (c + i + 1 >= lo && c + i + 1 <= hi) ? __float_as_uint(s1) : 0xff800000u;
+                        w[i + 2] = (c + i + 2 >= lo && c + i + 2 <= hi) ? __float_as_uint(s2) : 0xff800000u;
+                        w[i + 3] = (c + i + 3 >= lo && c + i + 3 <= hi) ? __float_as_uint(s3) : 0xff800000u;
                     }
                     tmem_st32(s_addr + c, w);
                 }
@@ -587,6 +622,19 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_read[t]);   // the scores are in registers: their columns may go to the next job
+            if (whole && capped) {
+                const uint64_t cap_in = pair(p.scale_over_cap * (2.f * LOG2E), p.scale_over_cap * (2.f * LOG2E));
+                const uint64_t cap_c = pair(p.cap_over_scale, p.cap_over_scale), cap_m2 = pair(-2.f * p.cap_over_scale, -2.f * p.cap_over_scale);
+#pragma unroll
+                for (int i = 0; i < 2 * BN; i += 4) {   // (a missing second tile's numbers are never used)
+                    float s0 = SCORE(i), s1 = SCORE(i + 1), s2 = SCORE(i + 2), s3 = SCORE(i + 3);
+                    cap4(s0, s1, s2, s3, cap_in, cap_c, cap_m2);
+                    v[i >> 5][i & 31] = __float_as_uint(s0);
+                    v[i >> 5][(i & 31) + 1] = __float_as_uint(s1);
+                    v[i >> 5][(i & 31) + 2] = __float_as_uint(s2);
+                    v[i >> 5][(i & 31) + 3] = __float_as_uint(s3);
+                }
+            }
             if (j > 0) {
                 // the MMAs of the pair before have read its probabilities and added into O: both may be written now
                 ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1));

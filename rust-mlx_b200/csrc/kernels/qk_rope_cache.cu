@@ -357,6 +357,77 @@ __global__ void __launch_bounds__(1024) qk_whole_norm_rope_cache_kernel(
         }
     }
 }
+
+// The same split, rotation and page write where nothing is normed, for bfloat16 rows whose sizes are all multiples of
+// eight: no staging and no sums.  A thread takes eight neighbouring numbers of a head; in the rotated part it takes the
+// eight they pair with as well (d and d + rotary_dim / 2) and writes both.  Cosines and sines come from the step's table
+// [token, rotary_dim] (cosines, then sines), in float.
+__global__ void __launch_bounds__(256) qk_part_rope_cache_bf16_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int row_stride, int rotary_dim, const float* __restrict__ cos_sin,
+    const int* __restrict__ positions, const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride,
+    int page_size, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ q_out,
+    int n_tokens, int nq, int nkv, int dq, int dv, int hd, int write_kv, int* __restrict__ status) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int half = rotary_dim >> 1;
+    const int rotated = half >> 3;                              // units of a head that hold a rotated pair of eights
+    const int per_head = rotated + ((hd - rotary_dim) >> 3);    // then the numbers that pass unchanged, then zeros up to hd
+    const int qk_units = (nq + nkv) * per_head;
+    const int per_token = qk_units + nkv * (hd >> 3);
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_tokens * per_token) return;
+    const int t = (int)(idx / per_token);
+    int u = (int)(idx - (long long)t * per_token);
+    const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+    const int pos = positions[t];
+    size_t slot = 0;                                            // the token's place in its page, in heads' rows
+    if (u >= nq * per_head) {
+        if (!write_kv) return;
+        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+        if (page < 0) {
+            atomicExch(status, 1);
+            return;
+        }
+        slot = (size_t)page * nkv;
+    }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    if (u < qk_units) {
+        const int head = u / per_head, w = u - head * per_head;
+        const __nv_bfloat16* src = row + (size_t)head * dq;     // (key heads follow the query heads in the row)
+        __nv_bfloat16* dst = head < nq ? q_out + ((size_t)t * nq + head) * hd
+                                       : k_pool + ((slot + (head - nq)) * page_size + pos % page_size) * hd;
+        if (w < rotated) {
+            const int d0 = w << 3;
+            const uint4 ra = *reinterpret_cast<const uint4*>(src + d0), rb = *reinterpret_cast<const uint4*>(src + d0 + half);
+            const float* cs = cos_sin + (size_t)t * rotary_dim + d0;
+            const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(cs + half), s1 = *reinterpret_cast<const float4*>(cs + half + 4);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(&ra);
+            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&rb);
+            uint4 oa, ob;
+            __nv_bfloat16* pa = reinterpret_cast<__nv_bfloat16*>(&oa);
+            __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&ob);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float x = __bfloat162float(a[i]), y = __bfloat162float(b[i]);
+                pa[i] = __float2bfloat16_rn(x * c[i] - y * sn[i]);
+                pb[i] = __float2bfloat16_rn(y * c[i] + x * sn[i]);
+            }
+            *reinterpret_cast<uint4*>(dst + d0) = oa;
+            *reinterpret_cast<uint4*>(dst + d0 + half) = ob;
+        } else {
+            const int d0 = rotary_dim + ((w - rotated) << 3);
+            *reinterpret_cast<uint4*>(dst + d0) = d0 < dq ? *reinterpret_cast<const uint4*>(src + d0) : zero;
+        }
+    } else if (v_pool != nullptr) {
+        u -= qk_units;
+        const int head = u / (hd >> 3), d0 = (u - head * (hd >> 3)) << 3;
+        __nv_bfloat16* dst = v_pool + ((slot + head) * page_size + pos % page_size) * hd + d0;
+        *reinterpret_cast<uint4*>(dst) = d0 < dv ? *reinterpret_cast<const uint4*>(row + (size_t)(nq + nkv) * dq + (size_t)head * dv + d0) : zero;
+    }
+}
 }  // namespace
 
 RMX_API int rmx_qk_whole_norm_rope_cache(const void* qkv, int row_stride, const float* q_norm, const float* k_norm, float eps,
@@ -373,6 +444,16 @@ RMX_API int rmx_qk_whole_norm_rope_cache(const void* qkv, int row_stride, const 
     const size_t smem = (size_t)(nq + nkv) * dq * sizeof(float);
     RMX_REQUIRE(smem <= 200 * 1024, "qk_whole_norm_rope_cache: a projection of %d numbers is beyond 51200", (nq + nkv) * dq);
     cudaStream_t s = (cudaStream_t)stream;
+    const bool eights = dq % 8 == 0 && dv % 8 == 0 && hd % 8 == 0 && rotary_dim % 16 == 0 && row_stride % 8 == 0 &&
+                        ((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q_out | (uintptr_t)cos_sin) % 16 == 0;
+    if (dtype == RMX_BF16 && q_norm == nullptr && k_norm == nullptr && eights && (rotary_dim == 0 || cos_sin != nullptr)) {
+        const long long units = (long long)n_tokens * ((nq + nkv) * (rotary_dim / 16 + (hd - rotary_dim) / 8) + nkv * (hd / 8));
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_part_rope_cache_bf16_kernel, dim3((unsigned)((units + 255) / 256)), dim3(256), 0, s,
+            (const __nv_bfloat16*)qkv, row_stride, rotary_dim, cos_sin, positions, seq_index, block_table, table_stride, page_size,
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, dq, dv, hd, write_kv, status),
+            "qk_part_rope_cache");
+        return 0;
+    }
     if (dtype == RMX_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(qk_whole_norm_rope_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         RMX_CHECK_LAUNCHED(launch_dependent(qk_whole_norm_rope_cache_kernel<float>, dim3(n_tokens), dim3(256), smem, s, (const float*)qkv, row_stride,
