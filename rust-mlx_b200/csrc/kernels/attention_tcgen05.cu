@@ -258,7 +258,10 @@ struct Params {
 // One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
 // every key and value tile the block fetches, and while the softmax warps of one tile work the tensor cores
 // serve the other.
-template <int HD>
+// CAPPED: scores go through softcap * tanh(s / softcap).  A kernel of its own, so that the kernel without a cap does not
+// carry the cap's code in its loop over key pairs: skipped, it still cost that kernel four tenths of its time when the
+// kernel ran between other kernels (its code fetched anew), though nothing when it ran back to back.
+template <int HD, bool CAPPED>
 __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v,
@@ -586,7 +589,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             // Scores that go through softcap * tanh(s / softcap) are capped in raw units, so that all that follows stays
             // as it is: in that loop for a pair that is masked anyway, in registers after the load (below) for a whole one.
             const bool whole = __all_sync(0xffffffffu, row_ok && k0 + tiles * BN - 1 <= row_pos && k0 >= row_lo);
-            const bool capped = p.cap_over_scale > 0.f;
+            constexpr bool capped = CAPPED;
             if (!whole) {
                 // key k0 + i is seen if lo <= i <= hi
                 const int lo = row_lo - k0, hi = row_ok ? min(row_pos - k0, tiles * BN - 1) : -1 << 20;
@@ -622,7 +625,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_read[t]);   // the scores are in registers: their columns may go to the next job
-            if (whole && capped) {
+            if constexpr (CAPPED) if (whole) {
                 const uint64_t cap_in = pair(p.scale_over_cap * (2.f * LOG2E), p.scale_over_cap * (2.f * LOG2E));
                 const uint64_t cap_c = pair(p.cap_over_scale, p.cap_over_scale), cap_m2 = pair(-2.f * p.cap_over_scale, -2.f * p.cap_over_scale);
 #pragma unroll
@@ -917,21 +920,21 @@ int q_map(CUtensorMap* map, const void* base, long long tokens, int nq, int grou
     g_maps.emplace(key, *map);
     return 0;
 }
-template <int HD>
+template <int HD, bool CAPPED>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int n_tiles, int first_token,
            int run_tokens, cudaStream_t stream) {
     constexpr size_t smem = 1024 + (size_t)(HD / 64) * (2 * Q_BOX + (K_SLOTS + V_SLOTS) * KV_BOX);
     static bool raised[64] = {};
     if (rmx_first_on_device(raised)) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, CAPPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RMX_FAIL("attention_tcgen05: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
         cudaFuncAttributes fa;
-        e = cudaFuncGetAttributes(&fa, attention_tcgen05_kernel<HD>);
+        e = cudaFuncGetAttributes(&fa, attention_tcgen05_kernel<HD, CAPPED>);
         if (e != cudaSuccess || fa.numRegs != LAUNCH_REGS)   // the trade of registers between the warpgroups is worked out for this number
             RMX_FAIL("attention_tcgen05: built with %d registers a thread, not %d", e == cudaSuccess ? fa.numRegs : -1, LAUNCH_REGS);
     }
     // blocks are handed to the SMs in the order x, then y: all kv heads of the tile that sees the most keys first
-    attention_tcgen05_kernel<HD><<<dim3(p.nkv, n_tiles, p.n_splits), THREADS, smem, stream>>>(mq, mk, mv, p);
+    attention_tcgen05_kernel<HD, CAPPED><<<dim3(p.nkv, n_tiles, p.n_splits), THREADS, smem, stream>>>(mq, mk, mv, p);
     RMX_CHECK_LAUNCH("attention_tcgen05");
     if (p.n_splits > 1) {
         attention_tcgen05_merge_kernel<HD><<<(run_tokens * p.nq + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, p.n_rows, p.n_splits,
@@ -994,6 +997,9 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     if (pool_map(&mv, v_pool, pool_rows, p.box_rows, hd) != 0) return -1;
     if (n_splits > 1)
         RMX_REQUIRE(first_token >= 0 && run_tokens > 0 && first_token + run_tokens <= n_tokens, "attention_tcgen05: the tokens of this launch are not among the step's");
-    return hd == 64 ? launch<64>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream)
-                    : launch<128>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream);
+    if (p.cap_over_scale > 0.f)
+        return hd == 64 ? launch<64, true>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream)
+                        : launch<128, true>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream);
+    return hd == 64 ? launch<64, false>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream)
+                    : launch<128, false>(mq, mk, mv, p, n_tiles, first_token, run_tokens, (cudaStream_t)stream);
 }

@@ -227,6 +227,67 @@ def test_the_cap_bounds_a_score_and_the_sink_takes_its_share():
         close(out.view(nq, hd), vs[0][0].double().expand(nq, hd) * share, "float32", (s_raw, cap))
 
 
+@pytest.mark.parametrize("nq, nkv, dq, dv, hd, rot, page, pad", [
+    (4, 2, 64, 64, 64, 32, 16, 0), (6, 3, 48, 24, 64, 16, 8, 8), (2, 2, 128, 128, 128, 128, 64, 0), (8, 1, 32, 40, 48, 0, 16, 16),
+    (3, 1, 24, 24, 24, 8, 8, 0), (2, 2, 20, 12, 20, 20, 4, 3)])
+@pytest.mark.parametrize("write", [True, False])
+def test_unnormed_projection_split_rotated_and_written(nq, nkv, dq, dv, hd, rot, page, pad, write):
+    """Rows [q | k | v] of a wider buffer, no norms: q heads (rotated over their first ``rot`` numbers, halves paired, padded
+    with zeros to ``hd``) to their rows, k and v heads into the pages of tokens at scattered positions; every other place of
+    the pools keeps its NaN.  Sizes in eights take the kernel of eight numbers a thread, the others the general one."""
+    dt = torch.bfloat16
+    lengths, new = [37, 5, 130], [9, 5, 1]
+    starts = [n - c for n, c in zip(lengths, new)]
+    n = sum(new)
+    cols = (nq + nkv) * dq + nkv * dv
+    buf = (rnd((n, cols + pad), 5) * 3).to(dt).to(DEV)
+    qkv = buf[:, :cols]
+    positions = torch.tensor([s + i for s, c in zip(starts, new) for i in range(c)], dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor([j for j, c in enumerate(new) for _ in range(c)], dtype=torch.int32, device=DEV)
+    pages = [-(-L // page) for L in lengths]
+    order = torch.randperm(sum(pages), generator=torch.Generator().manual_seed(nq)).tolist()
+    table = torch.full((len(lengths), max(pages)), -1, dtype=torch.int32)
+    for j, c in enumerate(pages):
+        table[j, :c] = torch.tensor([order.pop() for _ in range(c)])
+    table = table.to(DEV)
+    k_pool = torch.full((sum(pages), nkv, page, hd), float("nan"), dtype=dt, device=DEV)
+    v_pool = torch.full_like(k_pool, float("nan"))
+    q_out = torch.full((n, nq * hd), float("nan"), dtype=dt, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    inv_freq = (1000.0 ** (-torch.arange(rot // 2, dtype=F) * 2 / max(rot, 1))).float().to(DEV) if rot else None
+    cos_sin = None
+    if rot:
+        cos_sin = torch.empty(n, rot, dtype=torch.float32, device=DEV)
+        ops().rope_table(positions, inv_freq, rot, cos_sin, 1.25)
+    ops().qk_whole_norm_rope_cache(qkv, None, None, 0.0, inv_freq, rot, positions, seq_index, table, page, k_pool, v_pool, q_out,
+                                   nq, nkv, dq, dv, hd, write, status, cos_sin)
+    assert status.item() == 0
+    x = qkv.double().cpu()
+    heads = x[:, :(nq + nkv) * dq].reshape(n, nq + nkv, dq).clone()
+    if rot:
+        ang = positions.double().cpu()[:, None] * inv_freq.double().cpu()[None, :]
+        cs, sn = (1.25 * torch.cos(ang))[:, None, :], (1.25 * torch.sin(ang))[:, None, :]
+        a, b = heads[..., :rot // 2].clone(), heads[..., rot // 2:rot].clone()
+        heads[..., :rot // 2], heads[..., rot // 2:rot] = a * cs - b * sn, b * cs + a * sn
+    want_q = torch.zeros(n, nq, hd, dtype=F)
+    want_q[..., :dq] = heads[:, :nq]
+    close(q_out.reshape(n, nq, hd), want_q, "bfloat16")
+    assert (q_out.reshape(n, nq, hd)[..., dq:] == 0).all()
+    seen = torch.zeros(k_pool.shape[0], page, dtype=torch.bool)
+    if write:
+        for t in range(n):
+            pos, pg = int(positions[t]), int(table[int(seq_index[t]), int(positions[t]) // page])
+            seen[pg, pos % page] = True
+            want_k = torch.zeros(nkv, hd, dtype=F)
+            want_k[:, :dq] = heads[t, nq:]
+            close(k_pool[pg, :, pos % page], want_k, "bfloat16")
+            want_v = torch.zeros(nkv, hd, dtype=F)
+            want_v[:, :dv] = x[t, (nq + nkv) * dq:].reshape(nkv, dv)
+            assert torch.equal(v_pool[pg, :, pos % page].double().cpu(), want_v)
+    untouched = ~seen[:, None, :, None].expand(-1, nkv, -1, hd)
+    assert torch.isnan(k_pool.cpu()[untouched]).all() and torch.isnan(v_pool.cpu()[untouched]).all()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, dim, r, rot, row, page, neighbours", [(2, 16, 24, 8, 32, 16, True), (5, 6, 20, 6, 32, 4, True), (8, 32, 64, 64, 128, 64, True),
                                                                       (3, 8, 10, 4, 16, 8, False), (1, 4, 96, 32, 128, 16, True), (2, 14, 18, 2, 32, 8, True)])
