@@ -479,9 +479,9 @@ GUGALORN_PHASES = {"norm1": "add + norm", "norm2": "add + norm", "conv_in": "inp
 def sosuvik_shape(width, heads, kv_heads, dim, rot, kv_rank, rot_dim, experts, top, expert_ff, route_groups, keep, vocab, chunk, groups=1):
     """Four layer runs a group: attention whose chunk is longer than any context here, a latent layer, (in the first
     group the same latent layer again: a loop of two passes; elsewhere a second one), attention in chunks of ``chunk``."""
-    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    scaling = {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}
     mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
-           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": route_groups, "keep": keep}}}
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": route_groups, "keep": keep}}}
 
     def attention(size):
         return {"type": "attention", "mlp": mlp,
@@ -493,14 +493,14 @@ def sosuvik_shape(width, heads, kv_heads, dim, rot, kv_rank, rot_dim, experts, t
     layers = [attention(4 * MAX_CONTEXT), latent, attention(chunk)]
     for _ in range(groups - 1):
         layers += [attention(4 * MAX_CONTEXT), latent, latent, attention(chunk)]
-    return {"architecture": "Sosuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+    return {"architecture": "Sosuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
             "loop": {"start": 1, "stop": 2, "times": 2}, "layers": layers}
 
 
 SOSUVIK_SIZES = {
-    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, kv_rank=96, rot_dim=32, experts=32, top=4, expert_ff=1024, route_groups=4,
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, kv_rank=112, rot_dim=16, experts=32, top=4, expert_ff=1024, route_groups=4,
                keep=2, vocab=32768, chunk=1024),
-    "4k": dict(width=4096, heads=16, kv_heads=4, dim=128, rot=64, kv_rank=96, rot_dim=32, experts=64, top=6, expert_ff=1408, route_groups=8,
+    "4k": dict(width=4096, heads=16, kv_heads=4, dim=128, rot=64, kv_rank=112, rot_dim=16, experts=64, top=6, expert_ff=1408, route_groups=8,
                keep=4, vocab=65536, chunk=1024),
 }
 

@@ -65,7 +65,7 @@ S1 = model(211, 64, [layer(attn(4, 2, 16, 24, rot(5000.0, 8, (4.0, 64, 8.0, 2.0)
 S2 = model(300, 96, [layer(attn(3, 3, 32, 32, rot(1e4, 32)), moe(48, 5, 5, 0.5)),
                      layer(lat(3, 8, 16, 16, 40, base=500.0), moe(32, 8, 1, 0.25, 0.5, (4, 1))),
                      layer(attn(6, 2, 16, 8, rot(1e6, 4), chunk=50), moe(16, 3, 2, 1.0, 3.0))], eps=1e-5)
-S3 = model(320, 128, [layer(attn(8, 2, 64, 64, rot(2e5, 32, (8.0, 128, 16.0, 1.0)), softcap=30.0, chunk=130), moe(128, 6, 2, 0.6, 2.0, (3, 2))),
+S3 = model(352, 128, [layer(attn(8, 2, 64, 64, rot(2e5, 32, (8.0, 128, 16.0, 1.0)), softcap=30.0, chunk=130), moe(128, 6, 2, 0.6, 2.0, (3, 2))),
                       layer(lat(8, 32, 64, 32, 64, base=3e5), moe(64, 4, 2, 0.5, 1.0, (2, 1))),
                       layer(attn(4, 4, 128, 128, rot(1e4, 128), chunk=64), None)],
            loop=(1, 2, 2), logit_scale=2.0)
