@@ -213,7 +213,10 @@ class GatedAttentionMixer(Mixer):
             if tap is not None:
                 tap("attn_gated", o)
         elif hd != self.vdim:
-            o = o.view(n, nq, hd)[:, :, :self.vdim].reshape(n, nq * self.vdim)
+            # (a copy into a buffer of its own: with one head, reshape would hand the product a view with gaps between rows)
+            narrow = ws.get("attn_narrow", (n, nq * self.vdim), dt)
+            narrow.view(n, nq, self.vdim).copy_(o.view(n, nq, hd)[:, :, :self.vdim])
+            o = narrow
         y = ws.get(self.out_name, (n, self.width), dt)
         ops.linear(o, self.w_o, y, ws, batch.status)
         if tap is not None:

@@ -442,7 +442,7 @@ CUTS = (11, 1, 2, 1, 1, 7, 1, 1, 2, 19, 1, 3)
 
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, dims, scaling, cap, chunk, page", [
     (4, 2, 16, 24, 8, (4.0, 64, 8.0, 2.0), 5.0, 12, 4), (3, 3, 8, 8, 8, None, 0.0, 0, 8), (6, 2, 16, 8, 4, None, 3.0, 5, 16),
-    (2, 1, 12, 20, 12, (2.0, 16, 4.0, 1.0), 0.0, 16, 16)])
+    (2, 1, 12, 20, 12, (2.0, 16, 4.0, 1.0), 0.0, 16, 16), (1, 1, 16, 8, 8, None, 0.0, 0, 8)])
 def test_attention_part_over_steps(heads, kv_heads, dim, vdim, dims, scaling, cap, chunk, page):
     from rust_mlx_b200.config.sosuvik import RotationConfig
     from rust_mlx_b200.parts.attention import GatedAttentionMixer
