@@ -3,5 +3,6 @@ from .qwen3 import Qwen3Config
 from .resolorn import ResolornConfig
 from .gugalorn import GugalornConfig
 from .sosuvik import SosuvikConfig
+from .reverax import ReveraxConfig
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "GugalornConfig", "SosuvikConfig", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "GugalornConfig", "SosuvikConfig", "ReveraxConfig", "read_config_json"]

@@ -9,7 +9,14 @@
 #pragma once
 #include "common.cuh"
 
-enum { RMX_ACT_SILU = 0, RMX_ACT_GELU_TANH = 1, RMX_ACT_SWISH_CLAMP = 2 };
+enum { RMX_ACT_SILU = 0, RMX_ACT_GELU_TANH = 1, RMX_ACT_SWISH_CLAMP = 2, RMX_ACT_RELU2 = 3, RMX_ACT_TANH = 4 };
+
+// One-argument activations, out = f(x):  act 3  squared relu: max(x, 0)^2 (a feed-forward without a gate);  act 4  tanh.
+__device__ __forceinline__ float unary_act(float x, int act) {
+    if (act == RMX_ACT_TANH) return tanhf(x);
+    const float r = fmaxf(x, 0.f);
+    return act == RMX_ACT_RELU2 ? r * r : x;
+}
 
 __device__ __forceinline__ float gated_act(float g, float u, int act, float limit, float alpha) {
     if (act == RMX_ACT_GELU_TANH) {

@@ -149,10 +149,11 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits_in, int n_exper
 //   has one expert); only experts of the `keep` groups with the largest scores can be chosen (the others' c counts as
 //   minus infinity: c itself may be negative)
 //   the `top` largest c among those choose the experts (ties go to the lower expert, or group)
-//   weight_e = s_e / (sum of the chosen s + 1e-20) * scale
+//   weight_e = s_e / (sum of the chosen s + 1e-20) * scale, or with normalize == 0 the score as it is: s_e * scale
 // Everything in float.  Shared memory: per warp n_experts floats of c, n_experts of s, `groups` of group scores.
 __global__ void moe_group_topk_kernel(const float* __restrict__ logits_in, const float* __restrict__ correction, int n_experts, int top,
-                                      int groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights, int n_rows) {
+                                      int groups, int keep, float scale, int normalize, int* __restrict__ ids, float* __restrict__ weights,
+                                      int n_rows) {
     extern __shared__ float route_all[];
     allow_dependents();
     wait_for_prior_kernels();
@@ -228,7 +229,7 @@ __global__ void moe_group_topk_kernel(const float* __restrict__ logits_in, const
     for (int k = 0; k < top; ++k) total += __shfl_sync(0xffffffffu, mine, k);
     if (lane < top) {
         ids[(size_t)row * top + lane] = mine_id;
-        weights[(size_t)row * top + lane] = mine / (total + 1e-20f) * scale;
+        weights[(size_t)row * top + lane] = normalize ? mine / (total + 1e-20f) * scale : mine * scale;
     }
 }
 
@@ -338,7 +339,24 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
     }
 }
 
+// ---- rows into the experts' order, each times its weight ---------------------------------------------------------
+// out[p, :] = weights[pair] * x[pair / top, :] with pair = sorted[p]: for experts that are given the weighted row
+// instead of having their result weighted.  Float product, one rounding.
+template <typename T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ x, const int* __restrict__ sorted, const float* __restrict__ weights, int top,
+                                         T* __restrict__ out, int width, size_t total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t p = idx / width;
+    const int c = (int)(idx - p * width);
+    const int pair = sorted[p];
+    out[idx] = from_float<T>(weights[pair] * to_float(x[(size_t)(pair / top) * width + c]));
+}
+
 // ---- the weighted sum -----------------------------------------------------------------------------------------
+// (weights may be null: every choice counts once)
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ where, const float* __restrict__ weights,
                                    const T* __restrict__ shared_out, T* __restrict__ out, int top, int width, size_t total) {
@@ -350,7 +368,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
     const int col = (int)(idx - row * width);
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
-        acc = fmaf(weights[row * top + k], to_float(y[(size_t)where[row * top + k] * width + col]), acc);
+        acc = fmaf(weights ? weights[row * top + k] : 1.f, to_float(y[(size_t)where[row * top + k] * width + col]), acc);
     if (shared_out) acc += to_float(shared_out[idx]);
     out[idx] = from_float<T>(acc);
 }
@@ -370,7 +388,7 @@ __global__ void moe_combine8_kernel(const __nv_bfloat16* __restrict__ y, const i
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < top; ++k) {
-        const float wk = weights[row * top + k];
+        const float wk = weights ? weights[row * top + k] : 1.f;
         const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)where[row * top + k] * width + col);
         const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -406,7 +424,7 @@ __global__ void moe_combine8_kernel(const __nv_bfloat16* __restrict__ y, const i
 // moe_group_topk_kernel); correction may be null, groups 1 means no groups.
 RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int width, int n_experts, int top, int* ids,
                           float* weights, float* logits, int scoring, const float* correction, int groups, int keep,
-                          float route_scale, int dtype, void* stream) {
+                          float route_scale, int normalize, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(n_rows > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
                 "moe_route: %d of %d experts (at most 32 a row)", top, n_experts);
@@ -432,7 +450,7 @@ RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int 
     if (scoring == 1)
         RMX_CHECK_LAUNCHED(launch_dependent(moe_group_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32),
                                             (size_t)tw * (2 * n_experts + groups) * sizeof(float), s, (const float*)logits, correction, n_experts,
-                                            top, groups, keep, route_scale, ids, weights, n_rows), "moe_route");
+                                            top, groups, keep, route_scale, normalize, ids, weights, n_rows), "moe_route");
     else
         RMX_CHECK_LAUNCHED(launch_dependent(moe_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32), (size_t)tw * n_experts * sizeof(float), s,
                                             (const float*)logits, n_experts, top, ids, weights, n_rows), "moe_route");
@@ -477,7 +495,7 @@ RMX_API int rmx_moe_gemm(const void* A, int lda, const int* sorted, int divisor,
 RMX_API int rmx_moe_combine(const void* y, const int* where, const float* weights, const void* shared_out, void* out,
                             int n_rows, int top, int width, int dtype, void* stream) {
     if (n_rows == 0) return 0;
-    RMX_REQUIRE(n_rows > 0 && top > 0 && width > 0 && y && where && weights && out, "moe_combine: bad arguments");
+    RMX_REQUIRE(n_rows > 0 && top > 0 && width > 0 && y && where && out, "moe_combine: bad arguments");
     const size_t total = (size_t)n_rows * width;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
@@ -496,5 +514,23 @@ RMX_API int rmx_moe_combine(const void* y, const int* where, const float* weight
                            "moe_combine");
     else
         RMX_FAIL("moe_combine: unknown dtype %d", dtype);
+    return 0;
+}
+
+RMX_API int rmx_moe_gather_scaled(const void* x, const int* sorted, const float* weights, int top, void* out, int total, int width,
+                                  int dtype, void* stream) {
+    if (total == 0) return 0;
+    RMX_REQUIRE(total > 0 && top > 0 && width > 0 && x && sorted && weights && out, "moe_gather_scaled: bad sizes or a null pointer");
+    const size_t n = (size_t)total * width;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_gather_scaled_kernel<float>, grid, dim3(256), 0, s, (const float*)x, sorted, weights, top,
+                                            (float*)out, width, n), "moe_gather_scaled");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_gather_scaled_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, sorted,
+                                            weights, top, (__nv_bfloat16*)out, width, n), "moe_gather_scaled");
+    else
+        RMX_FAIL("moe_gather_scaled: unknown dtype %d", dtype);
     return 0;
 }

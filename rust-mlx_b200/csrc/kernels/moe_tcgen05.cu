@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_kernel(const __grid_const
                     if (n < p.N) {
 #pragma unroll
                         for (int t = 0; t < CH; ++t)
-                            if (c0 + t < rows) p.c[(size_t)(m0 + c0 + t) * p.ldc + n] = __float2bfloat16_rn(acc[t]);
+                            if (c0 + t < rows)
+                                p.c[(size_t)(m0 + c0 + t) * p.ldc + n] = __float2bfloat16_rn(p.epilogue == 2 ? unary_act(acc[t], p.act) : acc[t]);
                     }
                 }
             }
@@ -202,14 +203,15 @@ static int g_tile_variant = 0;
 RMX_API int rmx_moe_gemm_tcgen05_supports(int N, int K) { return N >= 1 && K >= 8 && K % 8 == 0; }
 
 // A [total, K] (rows lda apart) in sorted order, W [n_experts, N, K], C [total, N] or, with epilogue 1, [total, N / 2];
-// all bfloat16.  act, limit, alpha: the gated epilogue's activation (activation.cuh; epilogue 1 only).
+// all bfloat16.  act, limit, alpha: the gated epilogue's activation (activation.cuh; epilogue 1).  Epilogue 2: C = f(A W^T) number by
+// number with a one-argument activation (act 3: squared relu).
 RMX_API int rmx_moe_gemm_tcgen05(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, int n_experts,
                                  int total, int N, int K, int epilogue, int act, float limit, float alpha, int* status, void* stream) {
     if (total == 0 || N == 0) return 0;
     RMX_REQUIRE(total > 0 && n_experts > 0 && rmx_moe_gemm_tcgen05_supports(N, K), "moe_gemm_tcgen05: bad sizes total=%d N=%d K=%d", total, N, K);
     RMX_REQUIRE(lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "moe_gemm_tcgen05: operands must be 16-byte aligned");
-    RMX_REQUIRE(epilogue == 0 || (epilogue == 1 && N % 128 == 0), "moe_gemm_tcgen05: the gated epilogue needs N to be a multiple of 128, got %d", N);
-    RMX_REQUIRE(act >= 0 && act <= 2, "moe_gemm_tcgen05: unknown activation %d", act);
+    RMX_REQUIRE(epilogue == 0 || epilogue == 2 || (epilogue == 1 && N % 128 == 0), "moe_gemm_tcgen05: the gated epilogue needs N to be a multiple of 128, got %d", N);
+    RMX_REQUIRE(epilogue == 2 ? act == RMX_ACT_RELU2 : (act >= 0 && act <= 2), "moe_gemm_tcgen05: unknown activation %d for epilogue %d", act, epilogue);
     RMX_REQUIRE((long long)n_experts * N < (1ll << 31), "moe_gemm_tcgen05: too many weight rows");
     RMX_REQUIRE(offsets && status && C, "moe_gemm_tcgen05: a null pointer");
     // tiles of rows: 16 while experts have a row or two (decoding), 64, then 128

@@ -533,3 +533,127 @@ RMX_API int rmx_stream_concat(float* h, const void* delta, const void* delta2, f
         RMX_FAIL("stream_concat: unknown dtype %d", dtype);
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The stream's add and norm for layers that scale what they add number by number and norm the row in parts:
+//   v = h + va * (m1 * d1 + m2 * d2) + vb * d3        (float; any of d1, d2, d3, va, vb may be null: a null vector is ones)
+//   if (write_h) h = v
+//   the row is `groups` equal consecutive parts; part g is divided by sqrt(mean(part^2) + eps)
+//   x = that * w  (and x2 = that * w2 when a second weight is given), rounded once
+// One block a row (src = rows ? rows[r] : r), the row held in shared memory.  A part's squares are added by the warps
+// that the part falls to (warp i of the part takes numbers i*32 + lane, stepping by 32 * warps-a-part), each warp by the
+// butterfly, the warps in their order: the order follows the width, the number of parts and the block size, which the
+// width decides.
+template <typename T>
+__global__ void add_group_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ d1, const T* __restrict__ d2, const T* __restrict__ d3,
+                                         float m1, float m2, const float* __restrict__ va, const float* __restrict__ vb,
+                                         const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ x, int width,
+                                         int groups, int write_h, const float* __restrict__ w2, T* __restrict__ x2) {
+    extern __shared__ __align__(16) float gvals[];     // [width] the row, then [groups * warps_a_part] partial sums, then [groups]
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const size_t at = (size_t)src * width;
+    float* hrow = h + at;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = hrow[i];
+        if (d1) {
+            float a = m1 * to_float(d1[at + i]);
+            if (d2) a = fmaf(m2, to_float(d2[at + i]), a);
+            v += va ? va[i] * a : a;
+        }
+        if (d3) {
+            const float b = to_float(d3[at + i]);
+            v += vb ? vb[i] * b : b;
+        }
+        gvals[i] = v;
+        if (write_h) hrow[i] = v;
+    }
+    __syncthreads();
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wpp = warps >= groups ? warps / groups : 1;     // warps a part
+    const int size = width / groups;
+    float* part = gvals + width;
+    float* inv = part + groups * wpp;
+    for (int item = warp; item < groups * wpp; item += warps) {
+        const int g = item / wpp, sub = item - g * wpp;
+        const float* p = gvals + g * size;
+        float ss = 0.f;
+        for (int i = sub * 32 + lane; i < size; i += 32 * wpp) ss = fmaf(p[i], p[i], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) part[item] = ss;
+    }
+    __syncthreads();
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        float total = 0.f;
+        for (int sub = 0; sub < wpp; ++sub) total += part[g * wpp + sub];
+        inv[g] = rsqrtf(total / (float)size + eps);
+    }
+    __syncthreads();
+    T* xrow = x + (size_t)r * width;
+    T* xrow2 = w2 ? x2 + (size_t)r * width : nullptr;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float n = gvals[i] * inv[i / size];
+        xrow[i] = from_float<T>(n * w[i]);
+        if (xrow2) xrow2[i] = from_float<T>(n * w2[i]);
+    }
+}
+
+RMX_API int rmx_add_group_rmsnorm(float* h, const void* d1, const void* d2, const void* d3, float m1, float m2, const float* va,
+                                  const float* vb, const int* rows, const float* w, float eps, void* x, int n_rows, int width, int groups,
+                                  int write_h, const float* w2, void* x2, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && width > 0 && groups > 0 && width % groups == 0, "add_group_rmsnorm: %d numbers in %d parts", width, groups);
+    RMX_REQUIRE(d1 != nullptr || d2 == nullptr, "add_group_rmsnorm: a second term without a first");
+    RMX_REQUIRE(!(rows && write_h), "add_group_rmsnorm: rows and write_h do not go together");
+    RMX_REQUIRE((w2 == nullptr) == (x2 == nullptr), "add_group_rmsnorm: a second weight goes with a second output");
+    const int threads = block_threads(width);
+    const int warps = threads / 32, wpp = warps >= groups ? warps / groups : 1;
+    const size_t smem = ((size_t)width + (size_t)groups * wpp + groups) * sizeof(float);
+    RMX_REQUIRE(smem <= 200 * 1024, "add_group_rmsnorm: a row of %d numbers in %d parts needs too much shared memory", width, groups);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32) {
+        static bool raised[64] = {};
+        if (smem > 48 * 1024 && rmx_first_on_device(raised))
+            cudaFuncSetAttribute(add_group_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        RMX_CHECK_LAUNCHED(launch_dependent(add_group_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, h, (const float*)d1,
+                                            (const float*)d2, (const float*)d3, m1, m2, va, vb, rows, w, eps, (float*)x, width, groups,
+                                            write_h, w2, (float*)x2), "add_group_rmsnorm");
+    } else if (dtype == RMX_BF16) {
+        static bool raised[64] = {};
+        if (smem > 48 * 1024 && rmx_first_on_device(raised))
+            cudaFuncSetAttribute(add_group_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        RMX_CHECK_LAUNCHED(launch_dependent(add_group_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, h,
+                                            (const __nv_bfloat16*)d1, (const __nv_bfloat16*)d2, (const __nv_bfloat16*)d3, m1, m2, va, vb, rows,
+                                            w, eps, (__nv_bfloat16*)x, width, groups, write_h, w2, (__nv_bfloat16*)x2), "add_group_rmsnorm");
+    } else {
+        RMX_FAIL("add_group_rmsnorm: unknown dtype %d", dtype);
+    }
+    return 0;
+}
+
+// out = f(x) number by number, in float with one rounding (activation.cuh: squared relu, tanh); out may be x.
+template <typename T>
+__global__ void unary_act_kernel(const T* x, T* out, size_t total, int act) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    out[idx] = from_float<T>(unary_act(to_float(x[idx]), act));
+}
+
+RMX_API int rmx_unary_act(const void* x, void* out, long long total, int act, int dtype, void* stream) {
+    if (total == 0) return 0;
+    RMX_REQUIRE(total > 0 && (act == RMX_ACT_RELU2 || act == RMX_ACT_TANH), "unary_act: bad size or unknown activation %d", act);
+    const dim3 grid((unsigned)((total + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(unary_act_kernel<float>, grid, dim3(256), 0, s, (const float*)x, (float*)out, (size_t)total, act), "unary_act");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(unary_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                                            (size_t)total, act), "unary_act");
+    else
+        RMX_FAIL("unary_act: unknown dtype %d", dtype);
+    return 0;
+}

@@ -531,3 +531,152 @@ RMX_API int rmx_qk_rope_cache(const void* qkv, const float* q_norm, const float*
     RMX_CHECK_LAUNCH("qk_rope_cache");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The general split of a projection row [q (nq * dq) | k (nkv * dq) | v (nkv * dv)] into heads, for mixers whose options
+// the kernels above do not take together.  One warp a (token, head), everything in float, one rounding:
+//   + bias (float, as long as the row; or null)
+//   q, k: RMS norm over the head's dq numbers with a weight of dq numbers that all heads share (null: no norm)
+//   q, k: rotation of the first `rot` numbers by the step's table `cos_sin` [tokens][cos of pair j | sin of pair j];
+//         pairs are (j, j + rot / 2), or with `interleaved` neighbours (2j, 2j + 1)
+//   v:    with `v_cos_sin` (a table over dv numbers) the value is rotated too, over all its dv numbers, pairs as
+//         `v_interleaved` says: a value is then cached turned by its own position
+//   q goes to q_out [tokens, nq, hd], k and v into their pages; heads narrower than hd are padded with zeros.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32) heads_rope_cache_kernel(
+    const T* __restrict__ qkv, int row_stride, const float* __restrict__ bias, const float* __restrict__ q_norm,
+    const float* __restrict__ k_norm, float eps, const float* __restrict__ cos_sin, int rot, int interleaved,
+    const float* __restrict__ v_cos_sin, int v_interleaved, const int* __restrict__ positions, const int* __restrict__ seq_index,
+    const int* __restrict__ block_table, int table_stride, int page_size, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    T* __restrict__ q_out, int n_tokens, int nq, int nkv, int dq, int dv, int hd, int write_kv, int* __restrict__ status) {
+    extern __shared__ float smem[];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)n_tokens * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int head = (int)(item % heads_total);
+    float* buf = smem + warp * hd;
+    const int pos = positions[t];
+    int col, n, turn = rot, neighbours = interleaved;
+    const float* table = cos_sin;
+    const float* norm_w;
+    T* dst;
+    if (head < nq) {
+        col = head * dq; n = dq; norm_w = q_norm;
+        dst = q_out + ((size_t)t * nq + head) * hd;
+    } else {
+        const int kvh = (head - nq) % nkv;
+        const bool is_v = head >= nq + nkv;
+        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+        if (page < 0) {
+            if (lane == 0) atomicExch(status, 1);
+            return;
+        }
+        const size_t off = (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
+        dst = (is_v ? v_pool : k_pool) + off;
+        if (is_v) {
+            col = (nq + nkv) * dq + kvh * dv; n = dv; norm_w = nullptr;
+            table = v_cos_sin; turn = v_cos_sin ? dv : 0; neighbours = v_interleaved;
+        } else {
+            col = nq * dq + kvh * dq; n = dq; norm_w = k_norm;
+        }
+    }
+    const T* src = qkv + (size_t)t * row_stride + col;
+    float ss = 0.f;
+    for (int d = lane; d < n; d += 32) {
+        float v = to_float(src[d]);
+        if (bias) v += bias[col + d];
+        buf[d] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (norm_w) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)n + eps);
+        __syncwarp();
+        for (int d = lane; d < n; d += 32) buf[d] = buf[d] * inv * norm_w[d];
+    }
+    __syncwarp();
+    const int half = (table ? turn : 0) >> 1;
+    for (int j = lane; j < half; j += 32) {
+        const float cs = table[(size_t)t * turn + j], sn = table[(size_t)t * turn + half + j];
+        const int ia = neighbours ? 2 * j : j, ib = neighbours ? 2 * j + 1 : j + half;
+        const float a = buf[ia], b = buf[ib];
+        dst[ia] = from_float<T>(a * cs - b * sn);
+        dst[ib] = from_float<T>(b * cs + a * sn);
+    }
+    for (int d = 2 * half + lane; d < n; d += 32) dst[d] = from_float<T>(buf[d]);
+    for (int d = n + lane; d < hd; d += 32) dst[d] = from_float<T>(0.f);
+}
+
+// out[t, h, 0:dv] = o[t, h, 0:dv] turned by MINUS the token's angles (table [tokens][cos | sin] over dv numbers): what a
+// head gives when its values were cached turned by their own positions.  o's heads are hd numbers apart, out is dense.
+template <typename T>
+__global__ void unrotate_heads_kernel(const T* __restrict__ o, const float* __restrict__ cos_sin, int interleaved, T* __restrict__ out,
+                                      int heads, int dv, int hd, size_t total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int half = dv >> 1;
+    const size_t th = idx / half;
+    const int j = (int)(idx - th * half);
+    const size_t t = th / heads;
+    const float cs = cos_sin[t * dv + j], sn = cos_sin[t * dv + half + j];
+    const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+    const float a = to_float(o[th * hd + ia]), b = to_float(o[th * hd + ib]);
+    out[th * dv + ia] = from_float<T>(a * cs + b * sn);
+    out[th * dv + ib] = from_float<T>(b * cs - a * sn);
+}
+}  // namespace
+
+RMX_API int rmx_heads_rope_cache(const void* qkv, int row_stride, const float* bias, const float* q_norm, const float* k_norm, float eps,
+                                 const float* cos_sin, int rot, int interleaved, const float* v_cos_sin, int v_interleaved,
+                                 const int* positions, const int* seq_index, const int* block_table, int table_stride, int page_size,
+                                 void* k_pool, void* v_pool, void* q_out, int n_tokens, int nq, int nkv, int dq, int dv, int hd,
+                                 int write_kv, int* status, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(nq > 0 && nkv > 0 && dq > 0 && dv > 0 && hd >= dq && hd >= dv && hd <= MAX_HD, "heads_rope_cache: bad head sizes %d %d %d", dq, dv, hd);
+    RMX_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dq && (rot == 0 || cos_sin), "heads_rope_cache: %d rotated numbers of %d", rot, dq);
+    RMX_REQUIRE(v_cos_sin == nullptr || dv % 2 == 0, "heads_rope_cache: rotated values need an even size");
+    RMX_REQUIRE(page_size > 0 && table_stride > 0, "heads_rope_cache: bad page geometry");
+    const long long items = (long long)n_tokens * (nq + (write_kv ? 2 * nkv : 0));
+    const dim3 grid((unsigned)((items + WARPS - 1) / WARPS));
+    const size_t smem = (size_t)WARPS * hd * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(heads_rope_cache_kernel<float>, grid, dim3(WARPS * 32), smem, s, (const float*)qkv, row_stride, bias,
+                                            q_norm, k_norm, eps, cos_sin, rot, interleaved, v_cos_sin, v_interleaved, positions, seq_index,
+                                            block_table, table_stride, page_size, (float*)k_pool, (float*)v_pool, (float*)q_out, n_tokens, nq,
+                                            nkv, dq, dv, hd, write_kv, status), "heads_rope_cache");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(heads_rope_cache_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)qkv,
+                                            row_stride, bias, q_norm, k_norm, eps, cos_sin, rot, interleaved, v_cos_sin, v_interleaved,
+                                            positions, seq_index, block_table, table_stride, page_size, (__nv_bfloat16*)k_pool,
+                                            (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, n_tokens, nq, nkv, dq, dv, hd, write_kv, status),
+                           "heads_rope_cache");
+    else
+        RMX_FAIL("heads_rope_cache: unknown dtype %d", dtype);
+    return 0;
+}
+
+RMX_API int rmx_unrotate_heads(const void* o, const float* cos_sin, int interleaved, void* out, int n_tokens, int heads, int dv, int hd,
+                               int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(heads > 0 && dv > 0 && dv % 2 == 0 && hd >= dv && o && out && cos_sin && o != out, "unrotate_heads: bad sizes or pointers");
+    const size_t total = (size_t)n_tokens * heads * (dv / 2);
+    const dim3 grid((unsigned)((total + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(unrotate_heads_kernel<float>, grid, dim3(256), 0, s, (const float*)o, cos_sin, interleaved,
+                                            (float*)out, heads, dv, hd, total), "unrotate_heads");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(unrotate_heads_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)o, cos_sin,
+                                            interleaved, (__nv_bfloat16*)out, heads, dv, hd, total), "unrotate_heads");
+    else
+        RMX_FAIL("unrotate_heads: unknown dtype %d", dtype);
+    return 0;
+}

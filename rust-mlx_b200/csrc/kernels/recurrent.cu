@@ -213,6 +213,38 @@ __global__ void recurrence_prepare_gate_kernel(const T* __restrict__ q, int ld_q
     qf[idx] = qv;
 }
 
+// "decay" (linear attention with a learned decay a head and channel and a bonus for the current token):
+//   af = exp(-exp(raw w + w0)), kf = k, qf = r as floats in padded rows; bonus[t, h] = sum_c r_c u_c k_c (ascending c).
+template <typename T>
+__global__ void recurrence_prepare_decay_kernel(const T* __restrict__ r, int ld_r, const T* __restrict__ k, int ld_k,
+                                                const T* __restrict__ w, int ld_w, const float* __restrict__ w0, const float* __restrict__ u,
+                                                float* __restrict__ af, float* __restrict__ kf, float* __restrict__ qf,
+                                                float* __restrict__ bonus, int heads, int K, int kpt) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int row = rec_row(kpt), per_token = heads * row;
+    const int t = blockIdx.x, x = blockIdx.y * blockDim.x + threadIdx.x;     // grid (tokens, pieces of a token's rows)
+    if (x >= per_token) return;
+    const size_t idx = (size_t)t * per_token + x;
+    const int h = x / row, j = x - h * row;
+    const int c = rec_k_of(j, kpt);
+    float av = 0.f, kv = 0.f, qv = 0.f;
+    if (c >= 0 && c < K) {
+        av = expf(-expf(to_float(w[(size_t)t * ld_w + h * K + c]) + w0[h * K + c]));
+        kv = to_float(k[(size_t)t * ld_k + h * K + c]);
+        qv = to_float(r[(size_t)t * ld_r + h * K + c]);
+    }
+    af[idx] = av;
+    kf[idx] = kv;
+    qf[idx] = qv;
+    for (int hh = x; hh < heads; hh += per_token) {     // (the token's threads share out its heads' scalars)
+        float b = 0.f;
+        for (int i = 0; i < K; ++i)
+            b = fmaf(to_float(r[(size_t)t * ld_r + hh * K + i]) * u[hh * K + i], to_float(k[(size_t)t * ld_k + hh * K + i]), b);
+        bonus[(size_t)t * heads + hh] = b;
+    }
+}
+
 struct ScanArgs {
     float* state;           // [slots, heads, V, K]
     float* out;             // [tokens, heads * V]
@@ -224,6 +256,7 @@ struct ScanArgs {
     const void* v;          // [tokens, ld_v] of T, head h at columns h * V
     const float* v_scale;   // [tokens, heads] or null: v is multiplied with it
     const float* skip;      // [heads] or null: out += skip * (unscaled) v
+    const float* bonus;     // [tokens, heads] or null: out += bonus * (unscaled) v (the current token's own share, formed by the prepare kernel)
     int heads, row_heads, K, V, ld_v, steps;
 };
 
@@ -234,7 +267,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void st_global(float* p, float v) { asm volatile("st.global.f32 [%0], %1;\n" ::"l"(p), "f"(v)); }
 template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <typename T, int KPT, bool VEC>
+// PRE: a token's output is read from the state as the token finds it, o_t = S_(t-1)^T q_t, before the state is stepped (the
+// current token then enters through `bonus` alone).
+template <typename T, int KPT, bool VEC, bool PRE = false>
 __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) {
     extern __shared__ __align__(16) float rec_smem[];
     allow_dependents();
@@ -252,7 +287,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     const int K = A.K, V = A.V, H = A.heads, STEPS = A.steps;
     const int hk = h / (H / A.row_heads);           // the row that this head reads of kf and qf
     // one buffer: q rows, k rows, (a rows | a scalars), v (scaled), v (as it came)
-    const int buf_floats = STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS) + 2 * STEPS * cols;
+    const int buf_floats = STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS) + 2 * STEPS * cols + (PRE ? STEPS : 0);
     float* sbase = A.state + ((size_t)A.slots[seq] * H + h) * K * V;
     const T* vsrc = (const T*)A.v;
 
@@ -279,7 +314,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     const float skip = A.skip ? A.skip[h] : 0.f;
     const int n_chunks = (t1 - t0 + STEPS - 1) / STEPS;
     T vreg[MAXV];
-    float sreg[MAXV], areg = 0.f;
+    float sreg[MAXV], areg = 0.f, breg = 0.f;
 
     // the copies of a chunk's rows into buffer b, and its v (and scalars) into registers
     auto fetch = [&](int c) {
@@ -306,6 +341,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
             }
         }
         if (!VEC && threadIdx.x < ns) areg = A.af[(size_t)(ts + threadIdx.x) * H + h];
+        if (PRE && threadIdx.x < ns) breg = A.bonus[(size_t)(ts + threadIdx.x) * H + h];
     };
     // the registers of chunk c go into its buffer
     auto settle = [&](int c) {
@@ -320,6 +356,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
             }
         }
         if (!VEC && threadIdx.x < STEPS) buf[2 * STEPS * ROW + threadIdx.x] = areg;
+        if (PRE && threadIdx.x < STEPS) vs[2 * STEPS * cols + threadIdx.x] = breg;
     };
 
     if (n_chunks > 0) {
@@ -347,14 +384,20 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
                 const float4 a4 = VEC ? *reinterpret_cast<const float4*>(arow + i) : make_float4(a, a, a, a);
                 const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
                 const float4 q4 = *reinterpret_cast<const float4*>(qrow + i);
-                S[i] = fmaf(a4.x, S[i], k4.x * v.x);           acc[0] = fmaf(S[i], q4.x, acc[0]);
-                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v.x);   acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
-                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v.x);   acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
-                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v.x);   acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
-                S1[i] = fmaf(a4.x, S1[i], k4.x * v.y);         acc1[0] = fmaf(S1[i], q4.x, acc1[0]);
-                S1[i + 1] = fmaf(a4.y, S1[i + 1], k4.y * v.y); acc1[1] = fmaf(S1[i + 1], q4.y, acc1[1]);
-                S1[i + 2] = fmaf(a4.z, S1[i + 2], k4.z * v.y); acc1[2] = fmaf(S1[i + 2], q4.z, acc1[2]);
-                S1[i + 3] = fmaf(a4.w, S1[i + 3], k4.w * v.y); acc1[3] = fmaf(S1[i + 3], q4.w, acc1[3]);
+                if (PRE) {
+                    acc[0] = fmaf(S[i], q4.x, acc[0]);         acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                    acc[2] = fmaf(S[i + 2], q4.z, acc[2]);     acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+                    acc1[0] = fmaf(S1[i], q4.x, acc1[0]);      acc1[1] = fmaf(S1[i + 1], q4.y, acc1[1]);
+                    acc1[2] = fmaf(S1[i + 2], q4.z, acc1[2]);  acc1[3] = fmaf(S1[i + 3], q4.w, acc1[3]);
+                }
+                S[i] = fmaf(a4.x, S[i], k4.x * v.x);           if (!PRE) acc[0] = fmaf(S[i], q4.x, acc[0]);
+                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v.x);   if (!PRE) acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v.x);   if (!PRE) acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v.x);   if (!PRE) acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+                S1[i] = fmaf(a4.x, S1[i], k4.x * v.y);         if (!PRE) acc1[0] = fmaf(S1[i], q4.x, acc1[0]);
+                S1[i + 1] = fmaf(a4.y, S1[i + 1], k4.y * v.y); if (!PRE) acc1[1] = fmaf(S1[i + 1], q4.y, acc1[1]);
+                S1[i + 2] = fmaf(a4.z, S1[i + 2], k4.z * v.y); if (!PRE) acc1[2] = fmaf(S1[i + 2], q4.z, acc1[2]);
+                S1[i + 3] = fmaf(a4.w, S1[i + 3], k4.w * v.y); if (!PRE) acc1[3] = fmaf(S1[i + 3], q4.w, acc1[3]);
             }
             float o = (acc[0] + acc[1]) + (acc[2] + acc[3]), o1 = (acc1[0] + acc1[1]) + (acc1[2] + acc1[3]);
             o += __shfl_xor_sync(0xffffffffu, o, 1);   o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
@@ -364,8 +407,9 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
             // (stored as what it is, a store to global memory: through a generic pointer the compiler would have to assume
             // that it may change the rows in shared memory, and could not start the next token's reads before it)
             float* dst = A.out + ((size_t)(ts + s) * H + h) * V + vcol;
-            if (part == 0 && v_ok) st_global(dst, fmaf(skip, raw.x, o));
-            if (part == 1 && v_ok1) st_global(dst + 1, fmaf(skip, raw.y, o1));
+            const float own = PRE ? vs[2 * STEPS * cols + s] : skip;
+            if (part == 0 && v_ok) st_global(dst, fmaf(own, raw.x, o));
+            if (part == 1 && v_ok1) st_global(dst + 1, fmaf(own, raw.y, o1));
         }
         if (more) settle(c + 1);          // (the other buffer: nobody reads it before the next barrier)
         __syncthreads();
@@ -393,7 +437,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
 // rounded.
 template <typename T>
 __global__ void group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int ld_gate, const float* __restrict__ w,
-                                     int period, float eps, T* __restrict__ out, int ld_out, int groups, int size, float out_scale) {
+                                     int period, float eps, T* __restrict__ out, int ld_out, int groups, int size, float out_scale, int gate_after) {
     __shared__ float scratch[32];
     allow_dependents();
     wait_for_prior_kernels();
@@ -403,14 +447,16 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ y, const T* __res
     float ss = 0.f;
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
         float u = row[i];
-        if (grow) u *= siluf_(to_float(grow[i]));
+        if (grow && !gate_after) u *= siluf_(to_float(grow[i]));
         ss += u * u;
     }
     const float inv = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
         float u = row[i];
-        if (grow) u *= siluf_(to_float(grow[i]));
-        out[(size_t)t * ld_out + (size_t)g * size + i] = from_float<T>(u * inv * w[(g * size + i) % period] * out_scale);
+        if (grow && !gate_after) u *= siluf_(to_float(grow[i]));
+        float r = u * inv * w[(g * size + i) % period] * out_scale;
+        if (grow && gate_after) r *= siluf_(to_float(grow[i]));
+        out[(size_t)t * ld_out + (size_t)g * size + i] = from_float<T>(r);
     }
 }
 
@@ -419,7 +465,7 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ y, const T* __res
 template <typename T>
 __global__ void __launch_bounds__(128) group_rmsnorm4_kernel(const float* __restrict__ y, const T* __restrict__ gate, int ld_gate,
                                                              const float* __restrict__ w, int period, float eps, T* __restrict__ out,
-                                                             int ld_out, int groups, int size, float out_scale, int total) {
+                                                             int ld_out, int groups, int size, float out_scale, int total, int gate_after) {
     allow_dependents();
     wait_for_prior_kernels();
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -431,7 +477,7 @@ __global__ void __launch_bounds__(128) group_rmsnorm4_kernel(const float* __rest
     float ss = 0.f;
     for (int i = lane * 4; i < size; i += 128) {
         float4 u = *reinterpret_cast<const float4*>(row + i);
-        if (grow) {
+        if (grow && !gate_after) {
             u.x *= siluf_(to_float(grow[i])); u.y *= siluf_(to_float(grow[i + 1]));
             u.z *= siluf_(to_float(grow[i + 2])); u.w *= siluf_(to_float(grow[i + 3]));
         }
@@ -443,15 +489,17 @@ __global__ void __launch_bounds__(128) group_rmsnorm4_kernel(const float* __rest
     const float inv = rsqrtf(warp_sum(ss) / (float)size + eps) * out_scale;
     for (int i = lane * 4; i < size; i += 128) {
         float4 u = *reinterpret_cast<const float4*>(row + i);
-        if (grow) {
-            u.x *= siluf_(to_float(grow[i])); u.y *= siluf_(to_float(grow[i + 1]));
-            u.z *= siluf_(to_float(grow[i + 2])); u.w *= siluf_(to_float(grow[i + 3]));
+        float4 gt = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (grow) gt = make_float4(siluf_(to_float(grow[i])), siluf_(to_float(grow[i + 1])), siluf_(to_float(grow[i + 2])), siluf_(to_float(grow[i + 3])));
+        if (grow && !gate_after) {
+            u.x *= gt.x; u.y *= gt.y; u.z *= gt.z; u.w *= gt.w;
+            gt = make_float4(1.f, 1.f, 1.f, 1.f);
         }
         const float4 wv = *reinterpret_cast<const float4*>(w + (g * size + i) % period);
-        orow[i] = from_float<T>(u.x * inv * wv.x);
-        orow[i + 1] = from_float<T>(u.y * inv * wv.y);
-        orow[i + 2] = from_float<T>(u.z * inv * wv.z);
-        orow[i + 3] = from_float<T>(u.w * inv * wv.w);
+        orow[i] = from_float<T>(grow && gate_after ? u.x * inv * wv.x * gt.x : u.x * inv * wv.x);
+        orow[i + 1] = from_float<T>(grow && gate_after ? u.y * inv * wv.y * gt.y : u.y * inv * wv.y);
+        orow[i + 2] = from_float<T>(grow && gate_after ? u.z * inv * wv.z * gt.z : u.z * inv * wv.z);
+        orow[i + 3] = from_float<T>(grow && gate_after ? u.w * inv * wv.w * gt.w : u.w * inv * wv.w);
     }
 }
 
@@ -472,10 +520,44 @@ __global__ void sigmoid_gate_kernel(const T* o, int o_head, const T* __restrict_
     out[idx] = from_float<T>(v * sigmoidf_(to_float(gate[t * ld_gate + r])));
 }
 
+// What the mixes of a token with the token before it read:  out[s][t, c] = x[t, c] + (prev[t, c] - x[t, c]) * mu[s, c] for
+// s < n_mix, prev the row of the token before in the same sequence: of this step (t - 1), or `last` [slots, channels] (what
+// the sequence's last step left), or zeros at position 0.  Float, one rounding.  write_state: the thread of a sequence's
+// last token of the step stores its x into `last`; safe in this kernel only when every sequence brings one token (the
+// thread that writes the row is the one that read it), otherwise token_shift_state_kernel stores afterwards.
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, T* __restrict__ out, T* __restrict__ last,
+                                       int channels, int n_mix, const int* __restrict__ positions, const int* __restrict__ seq_index,
+                                       const int* __restrict__ slots, const int* __restrict__ q_start, size_t total, int write_state) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int)(idx / channels), c = (int)(idx - (size_t)t * channels);
+    const int seq = seq_index[t];
+    const float cur = to_float(x[idx]);
+    float prev = 0.f;
+    if (t > q_start[seq]) prev = to_float(x[idx - channels]);
+    else if (positions[t] > 0) prev = to_float(last[(size_t)slots[seq] * channels + c]);
+    const float d = prev - cur;
+    for (int s = 0; s < n_mix; ++s) out[(size_t)s * total + idx] = from_float<T>(fmaf(d, mu[(size_t)s * channels + c], cur));
+    if (write_state && t == q_start[seq + 1] - 1) last[(size_t)slots[seq] * channels + c] = x[idx];
+}
+
+template <typename T>
+__global__ void token_shift_state_kernel(const T* __restrict__ x, T* __restrict__ last, int channels, const int* __restrict__ slots,
+                                         const int* __restrict__ q_start, int n_seqs) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int seq = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels || q_start[seq + 1] <= q_start[seq]) return;
+    last[(size_t)slots[seq] * channels + c] = x[(size_t)(q_start[seq + 1] - 1) * channels + c];
+}
+
 static int rec_kpt(int K) { return K <= 32 ? 4 : (K <= 64 ? 8 : (K <= 128 ? 16 : 32)); }
 static int rec_steps(int kpt) { return kpt == 4 ? 16 : (kpt <= 16 ? 8 : 4); }
 
-template <typename T, bool VEC>
+template <typename T, bool VEC, bool PRE = false>
 int launch_scan(const ScanArgs& a, int n_seqs, int warps, cudaStream_t s) {
     const int cols = warps * REC_COLS;
     dim3 grid((a.V + cols - 1) / cols, a.heads, n_seqs), block(warps * 32);
@@ -483,12 +565,12 @@ int launch_scan(const ScanArgs& a, int n_seqs, int warps, cudaStream_t s) {
     const int kpt = rec_kpt(a.K);
     args.steps = rec_steps(kpt);
     const int row = rec_row(kpt);
-    const size_t smem = 2 * (size_t)(args.steps * row * 2 + (VEC ? args.steps * row : args.steps) + 2 * args.steps * cols) * sizeof(float);
+    const size_t smem = 2 * (size_t)(args.steps * row * 2 + (VEC ? args.steps * row : args.steps) + 2 * args.steps * cols + (PRE ? args.steps : 0)) * sizeof(float);
     switch (kpt) {
-        case 4: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 4, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
-        case 8: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 8, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
-        case 16: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 16, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
-        default: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 32, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+        case 4: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 4, VEC, PRE>, grid, block, smem, s, args), "recurrence_scan"); break;
+        case 8: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 8, VEC, PRE>, grid, block, smem, s, args), "recurrence_scan"); break;
+        case 16: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 16, VEC, PRE>, grid, block, smem, s, args), "recurrence_scan"); break;
+        default: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 32, VEC, PRE>, grid, block, smem, s, args), "recurrence_scan"); break;
     }
     return 0;
 }
@@ -554,7 +636,7 @@ RMX_API int rmx_linear_recurrence(int mode, float* state, float* out, const int*
     cudaStream_t s = (cudaStream_t)stream;
     ScanArgs a;
     a.state = state; a.out = out; a.q_start = q_start; a.slots = slots; a.kf = kf; a.qf = qf;
-    a.heads = heads; a.K = K; a.V = V; a.steps = 0;
+    a.heads = heads; a.K = K; a.V = V; a.steps = 0; a.bonus = nullptr;
     if (mode == 0) {
         RMX_REQUIRE(groups > 0 && heads % groups == 0 && s1, "linear_recurrence: %d heads in %d groups", heads, groups);
         const dim3 grid(n_tokens, (groups * row + threads - 1) / threads);
@@ -583,7 +665,7 @@ RMX_API int rmx_linear_recurrence(int mode, float* state, float* out, const int*
 }
 
 RMX_API int rmx_group_rmsnorm(const float* y, const void* gate, int ld_gate, const float* w, int period, float eps, void* out, int ld_out,
-                              int n_tokens, int groups, int size, float out_scale, int dtype, void* stream) {
+                              int n_tokens, int groups, int size, float out_scale, int gate_after, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && groups > 0 && size > 0 && period > 0 && y && w && out, "group_rmsnorm: bad sizes or a null pointer");
     RMX_REQUIRE((long long)n_tokens * groups < (1LL << 31), "group_rmsnorm: too many groups");
@@ -599,20 +681,20 @@ RMX_API int rmx_group_rmsnorm(const float* y, const void* gate, int ld_gate, con
         const dim3 grid4((unsigned)((total + 3) / 4));
         if (dtype == RMX_F32)
             RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm4_kernel<float>, grid4, dim3(128), 0, s, y, (const float*)gate, ld_gate, w, period, eps,
-                                                (float*)out, ld_out, groups, size, out_scale, total), "group_rmsnorm");
+                                                (float*)out, ld_out, groups, size, out_scale, total, gate_after), "group_rmsnorm");
         else if (dtype == RMX_BF16)
             RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm4_kernel<__nv_bfloat16>, grid4, dim3(128), 0, s, y, (const __nv_bfloat16*)gate, ld_gate,
-                                                w, period, eps, (__nv_bfloat16*)out, ld_out, groups, size, out_scale, total), "group_rmsnorm");
+                                                w, period, eps, (__nv_bfloat16*)out, ld_out, groups, size, out_scale, total, gate_after), "group_rmsnorm");
         else
             RMX_FAIL("group_rmsnorm: unknown dtype %d", dtype);
         return 0;
     }
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm_kernel<float>, grid, dim3(threads), 0, s, y, (const float*)gate, ld_gate, w, period, eps,
-                                            (float*)out, ld_out, groups, size, out_scale), "group_rmsnorm");
+                                            (float*)out, ld_out, groups, size, out_scale, gate_after), "group_rmsnorm");
     else if (dtype == RMX_BF16)
         RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, y, (const __nv_bfloat16*)gate, ld_gate,
-                                            w, period, eps, (__nv_bfloat16*)out, ld_out, groups, size, out_scale), "group_rmsnorm");
+                                            w, period, eps, (__nv_bfloat16*)out, ld_out, groups, size, out_scale, gate_after), "group_rmsnorm");
     else
         RMX_FAIL("group_rmsnorm: unknown dtype %d", dtype);
     return 0;
@@ -636,5 +718,64 @@ RMX_API int rmx_sigmoid_gate(const void* o, int o_head, const void* gate, int ld
                                             (const __nv_bfloat16*)gate, ld_gate, (__nv_bfloat16*)out, heads, vdim, total), "sigmoid_gate");
     else
         RMX_FAIL("sigmoid_gate: unknown dtype %d", dtype);
+    return 0;
+}
+
+// The "decay" form: per head and channel a_t = exp(-exp(w_t + w0)); o_t = S_(t-1)^T r_t + (sum_c r_c u_c k_c) v_t, then
+// S_t = diag(a_t) S_(t-1) + k_t v_t^T.  r, k, w: [tokens, heads * K] columns, v: [tokens, heads * V] columns, w0 and u float
+// [heads * K]; scratch af, kf, qf [tokens, heads, row] and bonus [tokens, heads].
+RMX_API int rmx_decay_recurrence(float* state, float* out, const int* q_start, const int* slots, int n_seqs, int n_tokens, int heads, int K,
+                                 int V, const void* r, int ld_r, const void* k, int ld_k, const void* w, int ld_w, const void* v, int ld_v,
+                                 const float* w0, const float* u, float* af, float* kf, float* qf, float* bonus, int warps, int dtype,
+                                 void* stream) {
+    if (n_seqs == 0 || n_tokens == 0) return 0;
+    RMX_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && heads > 0 && heads <= 65535 && K > 0 && V > 0 && n_tokens > 0, "decay_recurrence: bad sizes");
+    RMX_REQUIRE(K <= 256, "decay_recurrence: a state of %d rows a head is beyond 256", K);
+    RMX_REQUIRE(state && out && q_start && slots && r && k && w && v && w0 && u && af && kf && qf && bonus, "decay_recurrence: a null pointer");
+    RMX_REQUIRE(warps >= 1 && warps <= 8, "decay_recurrence: 1 to 8 warps a block");
+    RMX_REQUIRE(dtype == RMX_F32 || dtype == RMX_BF16, "decay_recurrence: unknown dtype %d", dtype);
+    const int kpt = rec_kpt(K), row = rec_row(kpt), threads = 256;
+    RMX_REQUIRE((heads * row + threads - 1) / threads <= 65535, "decay_recurrence: too many heads");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tokens, (heads * row + threads - 1) / threads);
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_decay_kernel<float>, grid, dim3(threads), 0, s, (const float*)r, ld_r, (const float*)k,
+                                            ld_k, (const float*)w, ld_w, w0, u, af, kf, qf, bonus, heads, K, kpt), "recurrence_prepare");
+    else
+        RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_decay_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const __nv_bfloat16*)r, ld_r,
+                                            (const __nv_bfloat16*)k, ld_k, (const __nv_bfloat16*)w, ld_w, w0, u, af, kf, qf, bonus, heads, K, kpt),
+                           "recurrence_prepare");
+    ScanArgs a;
+    a.state = state; a.out = out; a.q_start = q_start; a.slots = slots; a.kf = kf; a.qf = qf; a.af = af;
+    a.heads = heads; a.K = K; a.V = V; a.steps = 0; a.bonus = bonus; a.v = v; a.ld_v = ld_v; a.v_scale = nullptr; a.skip = nullptr;
+    a.row_heads = heads;
+    return dtype == RMX_F32 ? launch_scan<float, true, true>(a, n_seqs, warps, s) : launch_scan<__nv_bfloat16, true, true>(a, n_seqs, warps, s);
+}
+
+// x [tokens, channels] dense, mu float [n_mix, channels], out [n_mix, tokens, channels], last [slots, channels] of x's type.
+RMX_API int rmx_token_shift_mix(const void* x, const float* mu, void* out, void* last, int channels, int n_mix, const int* positions,
+                                const int* seq_index, const int* slots, const int* q_start, int n_tokens, int n_seqs, int single_tokens,
+                                int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(channels > 0 && n_mix > 0 && n_seqs > 0 && n_seqs <= 65535 && x && mu && out && last, "token_shift_mix: bad sizes or a null pointer");
+    const size_t total = (size_t)n_tokens * channels;
+    const dim3 grid((unsigned)((total + 255) / 256)), sgrid((channels + 255) / 256, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32) {
+        RMX_CHECK_LAUNCHED(launch_dependent(token_shift_mix_kernel<float>, grid, dim3(256), 0, s, (const float*)x, mu, (float*)out, (float*)last,
+                                            channels, n_mix, positions, seq_index, slots, q_start, total, single_tokens), "token_shift_mix");
+        if (!single_tokens)
+            RMX_CHECK_LAUNCHED(launch_dependent(token_shift_state_kernel<float>, sgrid, dim3(256), 0, s, (const float*)x, (float*)last, channels,
+                                                slots, q_start, n_seqs), "token_shift_state");
+    } else if (dtype == RMX_BF16) {
+        RMX_CHECK_LAUNCHED(launch_dependent(token_shift_mix_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, mu,
+                                            (__nv_bfloat16*)out, (__nv_bfloat16*)last, channels, n_mix, positions, seq_index, slots, q_start,
+                                            total, single_tokens), "token_shift_mix");
+        if (!single_tokens)
+            RMX_CHECK_LAUNCHED(launch_dependent(token_shift_state_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, s, (const __nv_bfloat16*)x,
+                                                (__nv_bfloat16*)last, channels, slots, q_start, n_seqs), "token_shift_state");
+    } else {
+        RMX_FAIL("token_shift_mix: unknown dtype %d", dtype);
+    }
     return 0;
 }

@@ -116,6 +116,7 @@ def add_bias(x, bias):
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamp": 2}
+UNARY_ACTIVATIONS = {"relu2": 3, "tanh": 4}     # one-argument activations: the square of max(x, 0) (an expert without a gate), tanh
 
 
 def activation_args(activation, args=()) -> tuple:
@@ -244,16 +245,19 @@ def gate_heads(o, gate, heads, vdim):
 
 
 def moe_route(x, w_router, top, ids_out, weights_out, logits=None, scoring="softmax", correction=None, groups=1, keep=1,
-              route_scale=1.0):
+              route_scale=1.0, normalize=True):
     """Router of a mixture of experts: logits = x . w_router^T in float; per row the ``top`` largest choose the
     experts (ids_out [rows, top] int32), weights_out = softmax over the chosen logits.  ``logits``: [rows, experts]
     floats of scratch (made here if not given).
     ``scoring="sigmoid"``: an expert's score is sigmoid(logit); the choice goes by score + ``correction`` (float32 [experts]
     or None) among the experts of the ``keep`` best of ``groups`` equal groups of neighbours (a group's worth: the sum of its
-    two largest corrected scores); the weights are the chosen scores over their sum, times ``route_scale``."""
+    two largest corrected scores); the weights are the chosen scores over their sum, times ``route_scale``; with
+    ``normalize=False`` (sigmoid scoring) a weight is the chosen score itself, times ``route_scale``."""
     lib = kernels_library()
     n, width = x.shape
     e = w_router.shape[0]
+    if not normalize and scoring != "sigmoid":
+        raise KernelError("moe_route: weights that are not normalised go with sigmoid scoring")
     if w_router.shape != (e, width) or ids_out.shape != (n, top) or weights_out.shape != (n, top):
         raise KernelError("moe_route: shapes do not fit")
     if logits is None:
@@ -268,7 +272,7 @@ def moe_route(x, w_router, top, ids_out, weights_out, logits=None, scoring="soft
                             c_int(top), _ptr(ids_out, torch.int32, "ids"), _ptr(weights_out, torch.float32, "weights"),
                             _ptr(logits, torch.float32, "logits"), c_int(1 if scoring == "sigmoid" else 0),
                             _ptr(correction, torch.float32, "correction"), c_int(groups), c_int(keep), c_float(route_scale),
-                            c_int(dtype_code(x)), _stream()))
+                            c_int(1 if normalize else 0), c_int(dtype_code(x)), _stream()))
     _launched(2)
 
 
@@ -317,29 +321,35 @@ def moe_gather(x, sorted_pairs, top, out):
     _launched()
 
 
-def moe_gemm_tcgen05(a, w, out, offsets, status, gated=False, activation="silu", args=()):
+def moe_gemm_tcgen05(a, w, out, offsets, status, gated=False, activation="silu", args=(), unary=None):
     """The experts' products on the tcgen05 tensor cores (bfloat16): out[p] = w[e] . a[p] for every place p of expert
     e's run; ``a`` [places, K] in sorted order, ``w`` [experts, N, K].  ``gated``: an expert's rows come in blocks of 64
-    gate rows and their 64 up rows, and out [places, N / 2] = f(gate, up) (``activation_args``)."""
+    gate rows and their 64 up rows, and out [places, N / 2] = f(gate, up) (``activation_args``).  ``unary`` ("relu2"): out =
+    f(product) number by number."""
     lib = kernels_library()
     e, n, k = w.shape
     total = a.shape[0]
     if a.shape[1] != k or out.shape != (total, n // 2 if gated else n) or not w.is_contiguous() or a.stride(1) != 1:
         raise KernelError(f"moe_gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     code, limit, alpha = activation_args(activation, args)
+    epilogue = 1 if gated else 0
+    if unary is not None:
+        if gated:
+            raise KernelError("moe_gemm_tcgen05: a gated product takes no one-argument activation")
+        epilogue, code = 2, UNARY_ACTIVATIONS[unary]
     check(lib.rmx_moe_gemm_tcgen05(c_void_p(a.data_ptr()), c_int(a.stride(0)), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
                                    c_int(out.stride(0)), _ptr(offsets, torch.int32, "offsets"), c_int(e), c_int(total), c_int(n),
-                                   c_int(k), c_int(1 if gated else 0), c_int(code), c_float(limit), c_float(alpha), _ptr(status, torch.int32, "status"),
+                                   c_int(k), c_int(epilogue), c_int(code), c_float(limit), c_float(alpha), _ptr(status, torch.int32, "status"),
                                    _stream()))
     _launched()
 
 
 def moe_combine(y, where, weights, shared_out, out):
     """out[row] = sum over choices of weights[row, choice] * y[where[row, choice]] (+ shared_out[row]), summed in float
-    in the order of the choices."""
+    in the order of the choices.  ``weights`` None: every choice counts once (the rows were weighted on their way in)."""
     lib = kernels_library()
     n, width = out.shape
-    top = weights.shape[1]
+    top = where.numel() // n if weights is None else weights.shape[1]
     if y.shape != (n * top, width) or where.numel() != n * top or (shared_out is not None and shared_out.shape != out.shape):
         raise KernelError("moe_combine: shapes do not fit")
     check(lib.rmx_moe_combine(_ptr(y, out.dtype, "y"), _ptr(where, torch.int32, "where"), _ptr(weights, torch.float32, "weights"),
@@ -531,9 +541,10 @@ def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, 
     _launched(2)
 
 
-def group_rmsnorm(y, weight, eps, out, groups, gate=None, out_scale=1.0):
+def group_rmsnorm(y, weight, eps, out, groups, gate=None, out_scale=1.0, gate_after=False):
     """out = RMSNorm of each of a row's ``groups`` equal parts of u = y (* silu(gate)), times ``weight`` (as long as a row,
-    or as long as a part and shared by the parts), times ``out_scale``; y float32, out and gate in the compute dtype."""
+    or as long as a part and shared by the parts), times ``out_scale``; y float32, out and gate in the compute dtype.
+    ``gate_after``: the gate multiplies the normed and weighted numbers instead: norm(y) * weight * silu(gate)."""
     lib = kernels_library()
     n, total = y.shape
     if total % groups or out.shape != (n, total) or out.stride(1) != 1 or weight.numel() not in (total, total // groups) \
@@ -542,8 +553,159 @@ def group_rmsnorm(y, weight, eps, out, groups, gate=None, out_scale=1.0):
     check(lib.rmx_group_rmsnorm(_ptr(y, torch.float32, "y"), c_void_p(gate.data_ptr() if gate is not None else 0),
                                 c_int(gate.stride(0) if gate is not None else 0), _ptr(weight, torch.float32, "weight"),
                                 c_int(weight.numel()), c_float(eps), c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(n),
-                                c_int(groups), c_int(total // groups), c_float(out_scale), c_int(dtype_code(out)), _stream()))
+                                c_int(groups), c_int(total // groups), c_float(out_scale), c_int(1 if gate_after else 0), c_int(dtype_code(out)), _stream()))
     _launched()
+
+
+def add_group_rmsnorm(h, terms, weight, eps, groups, x_out, rows=None, write_h=True, weight2=None, x2_out=None):
+    """v = h + va * (m1 * d1 + m2 * d2) + vb * d3; h = v (if write_h); the row is normed in ``groups`` equal consecutive
+    parts, each over its own root mean square, and x_out = that * weight (x2_out = that * weight2).  ``terms`` =
+    (d1, d2, d3, m1, m2, va, vb): tensors of x_out's dtype or None, factors, float32 vectors of a row's length or None.
+    With ``rows`` the rows rows[r] are read, x_out[r] is written and h is left alone."""
+    lib = kernels_library()
+    d1, d2, d3, m1, m2, va, vb = terms
+    n, width = x_out.shape[0], h.shape[1]
+    for d in (d1, d2, d3):
+        if d is not None and (d.dtype != x_out.dtype or d.shape != h.shape):
+            raise KernelError("add_group_rmsnorm: what is added must have the stream's shape and the output's dtype")
+    if d1 is None and d2 is not None:
+        raise KernelError("add_group_rmsnorm: a second term goes with a first")
+    for v in (va, vb, weight, weight2):
+        if v is not None and v.shape != (width,):
+            raise KernelError("add_group_rmsnorm: vectors and weights are as long as a row")
+    if (weight2 is None) != (x2_out is None) or (x2_out is not None and (x2_out.shape != x_out.shape or x2_out.dtype != x_out.dtype)):
+        raise KernelError("add_group_rmsnorm: a second weight goes with a second output like the first")
+    check(lib.rmx_add_group_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(d1, name="d1"), _ptr(d2, name="d2"), _ptr(d3, name="d3"),
+                                    c_float(m1), c_float(m2), _ptr(va, torch.float32, "va"), _ptr(vb, torch.float32, "vb"),
+                                    _ptr(rows, torch.int32, "rows"), _ptr(weight, torch.float32, "weight"), c_float(eps),
+                                    _ptr(x_out, name="x"), c_int(n), c_int(width), c_int(groups),
+                                    c_int(1 if (write_h and rows is None) else 0), _ptr(weight2, torch.float32, "weight2"),
+                                    _ptr(x2_out, name="x2"), c_int(dtype_code(x_out)), _stream()))
+    _launched()
+
+
+def unary_act(x, out, activation):
+    """out = f(x) number by number (float, one rounding; out may be x); ``activation`` "relu2": the square of max(x, 0), or "tanh"."""
+    lib = kernels_library()
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("unary_act: shapes or dtypes do not fit")
+    check(lib.rmx_unary_act(_ptr(x, name="x"), _ptr(out, name="out"), ctypes.c_longlong(x.numel()), c_int(UNARY_ACTIVATIONS[activation]),
+                            c_int(dtype_code(x)), _stream()))
+    _launched()
+
+
+def moe_gather_scaled(x, sorted_pairs, weights, top, out):
+    """out[p] = weights[pair] * x[pair // top] with pair = sorted_pairs[p]: the layer's rows in the order of the experts'
+    runs, each times the weight of its (row, choice) pair (float product, one rounding)."""
+    lib = kernels_library()
+    total, width = out.shape
+    if x.shape[1] != width or sorted_pairs.numel() != total or weights.numel() != total or x.dtype != out.dtype:
+        raise KernelError("moe_gather_scaled: shapes do not fit")
+    check(lib.rmx_moe_gather_scaled(_ptr(x, name="x"), _ptr(sorted_pairs, torch.int32, "sorted"), _ptr(weights, torch.float32, "weights"),
+                                    c_int(top), _ptr(out, name="out"), c_int(total), c_int(width), c_int(dtype_code(x)), _stream()))
+    _launched()
+
+
+def heads_rope_cache(qkv, bias, q_norm, k_norm, eps, cos_sin, rot, interleaved, v_cos_sin, v_interleaved, positions, seq_index,
+                     block_table, page_size, k_pool, v_pool, q_out, nq, nkv, dq, dv, hd, write_kv, status):
+    """Rows of ``qkv`` are [q (nq * dq) | k (nkv * dq) | v (nkv * dv)].  ``bias`` (float32, a row long, or None) is added;
+    every q and k head is RMS-normed over its dq numbers with one weight of dq numbers for all heads (None: no norm) and
+    rotated over its first ``rot`` numbers by the table ``cos_sin`` [tokens, rot] (pairs (j, j + rot / 2), or neighbours
+    with ``interleaved``); with ``v_cos_sin`` [tokens, dv] every value head is rotated over all its numbers too.  q goes
+    to ``q_out`` [tokens, nq * hd], k and v into their pages, heads padded with zeros to ``hd``."""
+    lib = kernels_library()
+    n = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != (nq + nkv) * dq + nkv * dv or q_out.shape != (n, nq * hd):
+        raise KernelError("heads_rope_cache: qkv must be [tokens, q | k | v] with unit column stride, q_out [tokens, nq * hd]")
+    if bias is not None and bias.shape != (qkv.shape[1],):
+        raise KernelError("heads_rope_cache: the bias is as long as a row")
+    if (cos_sin is not None and cos_sin.shape != (n, rot)) or (v_cos_sin is not None and v_cos_sin.shape != (n, dv)):
+        raise KernelError("heads_rope_cache: a table of angles is [tokens, rotated numbers]")
+    check(lib.rmx_heads_rope_cache(
+        c_void_p(qkv.data_ptr()), c_int(qkv.stride(0)), _ptr(bias, torch.float32, "bias"), _ptr(q_norm, torch.float32, "q_norm"),
+        _ptr(k_norm, torch.float32, "k_norm"), c_float(eps), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rot if cos_sin is not None else 0),
+        c_int(1 if interleaved else 0), _ptr(v_cos_sin, torch.float32, "v_cos_sin"), c_int(1 if v_interleaved else 0),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(k_pool, qkv.dtype, "k_pool"), _ptr(v_pool, qkv.dtype, "v_pool"), _ptr(q_out, qkv.dtype, "q_out"), c_int(n), c_int(nq),
+        c_int(nkv), c_int(dq), c_int(dv), c_int(hd), c_int(1 if write_kv else 0), _ptr(status, torch.int32, "status"),
+        c_int(dtype_code(qkv)), _stream()))
+    _launched()
+
+
+def unrotate_heads(o, cos_sin, interleaved, out, heads, dv, hd):
+    """out[t, h, :dv] = o[t, h, :dv] turned by minus the token's angles (``cos_sin`` [tokens, dv]): o's heads are ``hd``
+    numbers apart, out is dense."""
+    lib = kernels_library()
+    n = o.shape[0]
+    if o.shape != (n, heads * hd) or out.shape != (n, heads * dv) or cos_sin.shape != (n, dv) or out.dtype != o.dtype:
+        raise KernelError("unrotate_heads: shapes do not fit")
+    check(lib.rmx_unrotate_heads(_ptr(o, name="o"), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(1 if interleaved else 0),
+                                 _ptr(out, name="out"), c_int(n), c_int(heads), c_int(dv), c_int(hd), c_int(dtype_code(o)), _stream()))
+    _launched()
+
+
+def attention_talk_plain(q, k_pool, v_pool, talk, positions, seq_index, block_table, page_size, out, nq, nkv, hd, dq, dv, window,
+                         scale, status):
+    """Attention whose scaled scores are mixed over the heads before the softmax, s'_h = sum_g talk[h, g] s_g, on the FMA
+    units: q [tokens, nq * hd], pools with heads of ``hd`` numbers (keys: the first dq, values: the first dv), talk float32
+    [nq, nq], out [tokens, nq * dv]."""
+    lib = kernels_library()
+    n = q.shape[0]
+    if q.shape != (n, nq * hd) or out.shape != (n, nq * dv) or talk.shape != (nq, nq) or out.dtype != q.dtype:
+        raise KernelError("attention_talk_plain: shapes do not fit")
+    check(lib.rmx_attention_talk(_ptr(q, name="q"), _ptr(k_pool, q.dtype, "k_pool"), _ptr(v_pool, q.dtype, "v_pool"),
+                                 _ptr(talk, torch.float32, "talk"), _ptr(positions, torch.int32, "positions"),
+                                 _ptr(seq_index, torch.int32, "seq_index"), _ptr(block_table, torch.int32, "block_table"),
+                                 c_int(block_table.shape[1]), c_int(page_size), _ptr(out, name="out"), c_int(n), c_int(nq), c_int(nkv),
+                                 c_int(hd), c_int(dq), c_int(dv), c_int(window), c_float(scale), _ptr(status, torch.int32, "status"),
+                                 c_int(dtype_code(q)), _stream()))
+    _launched()
+
+
+def token_shift_mix(x, mu, out, last, batch, slots):
+    """out[s] = x + (prev - x) * mu[s] for every mix s: ``x`` [tokens, channels], ``mu`` float32 [mixes, channels], ``out``
+    [mixes, tokens, channels]; prev is the row of the token before in the same sequence: of this step, or ``last``
+    [slots, channels] (what the sequence's last step left; written with the step's last rows), or zeros at position 0."""
+    lib = kernels_library()
+    n, channels = x.shape
+    mixes = mu.shape[0]
+    if mu.shape != (mixes, channels) or out.shape != (mixes, n, channels) or out.dtype != x.dtype or last.dtype != x.dtype \
+            or last.shape[1:] != (channels,):
+        raise KernelError("token_shift_mix: shapes or dtypes do not fit")
+    single = batch.max_q_len == 1
+    check(lib.rmx_token_shift_mix(_ptr(x, name="x"), _ptr(mu, torch.float32, "mu"), _ptr(out, name="out"), _ptr(last, name="last"),
+                                  c_int(channels), c_int(mixes), _ptr(batch.positions, torch.int32, "positions"),
+                                  _ptr(batch.seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
+                                  _ptr(batch.q_start, torch.int32, "q_start"), c_int(n), c_int(batch.n_seqs), c_int(1 if single else 0),
+                                  c_int(dtype_code(x)), _stream()))
+    _launched(1 if single else 2)
+
+
+def recurrence_decay(r, k, w, v, w0, u, state, out, batch, slots, heads, kdim, vdim, workspace=None, warps=None):
+    """Per head and channel a_t = exp(-exp(w_t + w0)); o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, then
+    S_t = diag(a_t) S_(t-1) + k_t v_t^T: ``r``, ``k``, ``w`` [tokens, heads * kdim] (columns of wider rows allowed), ``v``
+    [tokens, heads * vdim], ``w0`` and ``u`` float32 [heads * kdim], ``state`` float32 [slots, heads, vdim, kdim]
+    (transposed), ``out`` float32 [tokens, heads * vdim]."""
+    lib = kernels_library()
+    n = r.shape[0]
+    hk = heads * kdim
+    if r.shape != (n, hk) or k.shape != (n, hk) or w.shape != (n, hk) or v.shape != (n, heads * vdim) or out.shape != (n, heads * vdim) \
+            or state.shape[1:] != (heads, vdim, kdim) or w0.numel() != hk or u.numel() != hk or len({r.dtype, k.dtype, w.dtype, v.dtype}) != 1:
+        raise KernelError("recurrence_decay: shapes or dtypes do not fit")
+    kf, qf, af, _ = _recurrence_scratch(workspace, n, heads, heads, kdim, True)
+    ws = workspace if workspace is not None else _own_workspace()
+    bonus = ws.get("recurrence_bonus", (n, heads), torch.float32)
+    p0, l0 = _cols(r, "r")
+    p1, l1 = _cols(k, "k")
+    p2, l2 = _cols(w, "w")
+    p3, l3 = _cols(v, "v")
+    check(lib.rmx_decay_recurrence(_ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
+                                   _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
+                                   c_int(n), c_int(heads), c_int(kdim), c_int(vdim), p0, l0, p1, l1, p2, l2, p3, l3,
+                                   _ptr(w0, torch.float32, "w0"), _ptr(u, torch.float32, "u"), _ptr(af), _ptr(kf), _ptr(qf), _ptr(bonus),
+                                   c_int(warps or _recurrence_warps(batch, heads, vdim)), c_int(dtype_code(r)), _stream()))
+    _launched(2)
 
 
 def sample(logits, temperature, uniform, out, slots=None, last_tokens=None):
@@ -1113,6 +1275,12 @@ class Kernels:
             return
         attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
                         window, scale, batch.status, sinks, chunk, softcap)
+
+    def attention_talk(self, q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dq, dv, window, scale,
+                       workspace=None):
+        """Attention whose scores are mixed over the heads before the softmax, over one step's batch."""
+        attention_talk_plain(q, k_pool, v_pool, talk, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
+                             dq, dv, window, scale, batch.status)
 
     def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype, chunk: int = 0) -> int:
         """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:

@@ -102,6 +102,12 @@ class ScaledSum:
     second: Optional[torch.Tensor] = None
     factor: float = 1.0
     ratio: float = 1.0
+    # a layer that scales what it adds number by number: vector * (factor * (first + ratio * second)) + third_vector * third,
+    # the vectors float32 of a row's length (None: ones), ``third`` a further tensor (None: nothing).  Only a norm that says
+    # so takes these (``GroupRMSNorm``); the others refuse them.
+    vector: Optional[torch.Tensor] = None
+    third: Optional[torch.Tensor] = None
+    third_vector: Optional[torch.Tensor] = None
 
     @staticmethod
     def weighted(a, wa: float, b, wb: float) -> "ScaledSum":

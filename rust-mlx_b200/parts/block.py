@@ -10,7 +10,7 @@ pending delta.
 """
 from __future__ import annotations
 
-from .base import Part, ScaledSum
+from .base import ParamSpec, Part, ScaledSum
 
 
 class PreNormBlock(Part):
@@ -67,10 +67,29 @@ class ParallelBlock(Part):
 
     graph_safe = True
 
-    def __init__(self, norm, mixer, ffn=None, factor: float = 1.0, norm2=None):
+    def __init__(self, norm, mixer, ffn=None, factor: float = 1.0, norm2=None, mixer_scale: str | None = None,
+                 ffn_scale: str | None = None, width: int = 0):
         if norm2 is not None and ffn is None:
             raise ValueError("a second norm goes with a feed-forward")
+        if ffn_scale is not None and ffn is None:
+            raise ValueError("a feed-forward's scale goes with a feed-forward")
+        if (mixer_scale is not None or ffn_scale is not None) and (width <= 0 or factor != 1.0):
+            raise ValueError("scale vectors need the width, and take the place of a factor")
         self.norm, self.mixer, self.ffn, self.factor, self.norm2 = norm, mixer, ffn, float(factor), norm2
+        # tensor names of learned vectors of the stream's width ("layer scale"): the mixer's result and the feed-forward's
+        # are each multiplied by its own, number by number, before they are added to the stream
+        self.mixer_scale, self.ffn_scale, self.width = mixer_scale, ffn_scale, int(width)
+        self.mixer_vector = self.ffn_vector = None
+
+    def param_specs(self):
+        return [ParamSpec(n, (self.width,), "norm", "float32") for n in (self.mixer_scale, self.ffn_scale) if n is not None]
+
+    def bind(self, tensors, ctx):
+        super().bind(tensors, ctx)
+        if self.mixer_scale is not None:
+            self.mixer_vector = tensors[self.mixer_scale].contiguous()
+        if self.ffn_scale is not None:
+            self.ffn_vector = tensors[self.ffn_scale].contiguous()
 
     def children(self):
         return [p for p in (self.norm, self.norm2, self.mixer, self.ffn) if p is not None]
@@ -91,11 +110,20 @@ class ParallelBlock(Part):
             if self.norm2 is not None:
                 tap("norm2", x_ffn)
         a = self.mixer.forward(x, batch, cache)
-        if tap is not None:
+        if tap is not None and not isinstance(a, ScaledSum):
             tap("mixer_out", a)
         m = None
         if self.ffn is not None:
             m = self.ffn.forward(x_ffn, batch)
             if tap is not None:
                 tap("ffn_out", m)
-        return h, ScaledSum(a, m, self.factor)
+        if self.mixer_vector is None and self.ffn_vector is None and not isinstance(a, ScaledSum):
+            return h, ScaledSum(a, m, self.factor)
+        # the mixer's share (itself perhaps a weighted sum of two mixers) under its vector, the feed-forward's under its own
+        if isinstance(a, ScaledSum):
+            if self.factor != 1.0:
+                raise ValueError("a mixer that hands on a weighted sum goes with scale vectors, not with a factor")
+            if a.vector is not None or a.third is not None:
+                raise ValueError("a mixer hands on at most two weighted terms")
+            return h, ScaledSum(a.first, a.second, a.factor, a.ratio, vector=self.mixer_vector, third=m, third_vector=self.ffn_vector)
+        return h, ScaledSum(a, None, 1.0, 1.0, vector=self.mixer_vector, third=m, third_vector=self.ffn_vector)

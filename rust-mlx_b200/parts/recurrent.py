@@ -145,6 +145,88 @@ class GatedLinearMixer(Mixer):
         return out
 
 
+class DecayLinearMixer(Mixer):
+    """Linear attention with a learned decay a head and channel and a bonus for the current token ("RWKV" time mixing):
+
+        every projection reads its own mix of the token's input and the previous token's: x + (x' - x) * mu_s, s in r, k, v, g, w
+        r, k, v = W_r, W_k, W_v of their mixes (heads x dim each), gate = silu(W_g mix_g)
+        a_t = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))                         per head and channel
+        o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t,  S_t = diag(a_t) S_(t-1) + k_t v_t^T
+
+    every head's o is RMS-normed over its own numbers, the heads side by side are multiplied by a weight and by the gate, and
+    projected out.  A request remembers the last token's input (compute dtype) and S (float32, zero at the start).  The
+    mixes, the decay, the state and the norm are float whatever the run's dtype."""
+
+    graph_safe = True
+    NAMES = {"mu": "mu.{s}", "r": "r", "k": "k", "v": "v", "g": "g", "w1": "w1", "w2": "w2", "w0": "w0", "u": "u", "norm": "norm", "out": "o"}
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, prefix: str, width: int, heads: int, dim: int, rank: int, eps: float, names: dict | None = None,
+                 out_name: str = "mixer_out"):
+        self.prefix, self.width = prefix, int(width)
+        self.heads, self.dim, self.rank, self.eps = int(heads), int(dim), int(rank), float(eps)
+        self.inner = self.heads * self.dim
+        self.names = {k: f"{prefix}.{v}" for k, v in {**self.NAMES, **(names or {})}.items()}
+        self.out_name = out_name
+
+    def cache_specs(self):
+        return [CacheSpec("state", state_shape=(self.width,), state_dtype="compute"),
+                CacheSpec("state", state_shape=(self.heads, self.dim, self.dim), state_dtype="float32")]
+
+    def param_specs(self):
+        n = self.names
+        specs = [ParamSpec(n["mu"].format(s=s), (self.width,), "linear", "float32") for s in self.MIXES]
+        specs += [ParamSpec(n[s], (self.inner, self.width)) for s in ("r", "k", "v", "g")]
+        specs += [ParamSpec(n["w1"], (self.rank, self.width)), ParamSpec(n["w2"], (self.inner, self.rank)),
+                  ParamSpec(n["w0"], (self.inner,), "linear", "float32"), ParamSpec(n["u"], (self.heads, self.dim), "linear", "float32"),
+                  ParamSpec(n["norm"], (self.inner,), "norm", "float32"), ParamSpec(n["out"], (self.width, self.inner))]
+        return specs
+
+    def bind(self, tensors, ctx):
+        super().bind(tensors, ctx)
+        n = self.names
+        self.mu = torch.stack([tensors.pop(n["mu"].format(s=s)) for s in self.MIXES]).contiguous()
+        self.w = {s: tensors[n[s]].contiguous() for s in ("r", "k", "v", "g", "w1", "w2")}
+        self.w0, self.u = tensors[n["w0"]].contiguous(), tensors[n["u"]].contiguous()
+        self.norm_w, self.w_out = tensors[n["norm"]].contiguous(), tensors[n["out"]].contiguous()
+
+    def linear_weights(self):
+        return list(self.w.values()) + [self.w_out]
+
+    def forward(self, x, batch, cache):
+        ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
+        last_cache, state_cache = cache
+        n, inner = x.shape[0], self.inner
+        tap = self.ctx.tap
+        mixes = ws.get("shift_mixes", (len(self.MIXES), n, self.width), dt)
+        ops.token_shift_mix(x, self.mu, mixes, last_cache.state, batch, last_cache.slots)
+        if tap is not None:
+            tap("shift_mixes", mixes)
+        proj = ws.get("decay_in", (5, n, inner), dt)       # r, k, v, g and the decay's raw numbers
+        for i, s in enumerate(("r", "k", "v", "g")):
+            ops.linear(mixes[i], self.w[s], proj[i], ws, batch.status)
+        low = ws.get("decay_low", (n, self.rank), dt)
+        ops.linear(mixes[4], self.w["w1"], low, ws, batch.status)
+        ops.unary_act(low, low, "tanh")
+        ops.linear(low, self.w["w2"], proj[4], ws, batch.status)
+        if tap is not None:
+            tap("decay_in", proj)
+        o = ws.get("decay_recurrence_out", (n, inner), torch.float32)
+        ops.recurrence_decay(proj[0], proj[1], proj[4], proj[2], self.w0, self.u, state_cache.state, o, batch, state_cache.slots,
+                             self.heads, self.dim, self.dim, workspace=ws)
+        if tap is not None:
+            tap("decay_recurrence_out", o)
+        normed = ws.get("decay_normed", (n, inner), dt)
+        ops.group_rmsnorm(o, self.norm_w, self.eps, normed, self.heads, gate=proj[3], gate_after=True)
+        if tap is not None:
+            tap("decay_normed", normed)
+        out = ws.get(self.out_name, (n, self.width), dt)
+        ops.linear(normed, self.w_out, out, ws, batch.status)
+        if tap is not None:
+            tap("decay_proj", out)
+        return out
+
+
 class ParallelMixer(Mixer):
     """Two mixers side by side on the same input: left_scale * left(x) + right_scale * right(x).  The sum is handed on
     unformed (``ScaledSum``): the norm that adds it to the stream forms it in float."""

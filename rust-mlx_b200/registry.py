@@ -8,6 +8,7 @@ the model type.  An entry's ``build`` turns a typed configuration into a
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable
 
@@ -60,7 +61,16 @@ def find_architecture(raw: dict) -> Architecture:
 def load_config(path: str) -> ModelConfig:
     """Read a folder's config.json into the typed configuration of its architecture."""
     raw = read_config_json(path)
-    return find_architecture(raw).config_class.from_dict(raw)
+    config = find_architecture(raw).config_class.from_dict(raw)
+    if hasattr(config, "sizes_from_tensors") and os.path.isdir(path):
+        # a family may leave a size to the checkpoint: the configuration is shown the shapes of the folder's tensors
+        from .weights.loader import index_folder
+        try:
+            entries, _ = index_folder(path)
+        except (OSError, ValueError):
+            entries = {}
+        config.sizes_from_tensors({name: tuple(e.shape) for name, e in entries.items()})
+    return config
 
 
 def build_model_spec(config: ModelConfig):
@@ -75,4 +85,4 @@ def _load_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from .models import gugalorn, qwen3, resolorn, sosuvik  # noqa: F401  (they register themselves)
+        from .models import gugalorn, qwen3, resolorn, reverax, sosuvik  # noqa: F401  (they register themselves)
