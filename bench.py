@@ -583,6 +583,105 @@ SOSUVIK_PHASES = {"norm1": "add + two norms", "loop_in": "stream beside the embe
                   "ffn_out": "weighted sum of the experts"}
 
 
+# --family reverax: the Reverax design (attention whose scores are mixed over the heads; windowed attention with turned values
+# and learned sinks beside linear attention with a learned decay; norms in groups with scale vectors; dense feed-forwards and
+# experts without a gate) at layer sizes of real models, beside the Gugalorn design (its closest relative here: softmax
+# attention beside a linear recurrence) and the Qwen3 dense decoder of equal width, depth, heads and feed-forward width.
+
+def reverax_shape(width, heads, kv_heads, dim, rot, right_heads, right_dim, rank, ff, experts, top, expert_ff, vocab, window, groups=1):
+    """Four layers a group: mixed-score attention with a dense feed-forward, a parallel layer with experts, the same layer's
+    tensors again with caches of their own, mixed-score attention with experts."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 1e6, "dims": rot}}
+    side = {"left": dict(att, softcap=30.0, mask={"size": window}, rot={"base": 1e6, "dims": rot}),
+            "right": {"heads": right_heads, "dim": right_dim, "rank": rank}, "left_scale": 1.2, "right_scale": 1.1}
+    layers = []
+    for g in range(groups):
+        layers += [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": ff}}, {"type": "parallel", "mixer": side, "mlp": moe},
+                   {"type": "parallel", "mixer": side, "mlp": moe, "weights_of": 4 * g + 1}, {"type": "attention", "mixer": att, "mlp": moe}]
+    return {"architecture": "Reverax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2}, "logit_scale": 2.0, "layers": layers}
+
+
+REVERAX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, right_heads=32, right_dim=64, rank=64, ff=8192, experts=32, top=4,
+               expert_ff=1024, vocab=32768, window=1024),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, rot=64, right_heads=64, right_dim=64, rank=64, ff=12288, experts=64, top=6,
+               expert_ff=1408, vocab=65536, window=1024),
+}
+
+
+def reverax_costs(raw, starts, counts):
+    """tap name -> function(layer) -> (bytes, flops on the tensor cores) of the kernels that end at that tap, or None."""
+    n, W, S = sum(counts), raw["width"], len(counts)
+    everything = sum(s + c for s, c in zip(starts, counts))
+
+    def att(layer):
+        return layer["mixer"] if layer["type"] == "attention" else layer["mixer"]["left"]
+
+    def side(f):
+        return lambda layer: f(layer["mixer"]["right"]) if layer["type"] == "parallel" else None
+
+    def mlp(kind, f):
+        return lambda layer: f(layer["mlp"]) if (layer.get("mlp") or {}).get("kind") == kind else None
+
+    def touched(f):
+        e, top = f["router"]["experts"], f["router"]["top"]
+        return e * (1.0 - (1.0 - top / e) ** n)
+
+    def attention(layer):
+        m = att(layer)
+        window = (m.get("mask") or {}).get("size", 0)
+        read = sum(min(s + c, window + c) if window else s + c for s, c in zip(starts, counts))
+        return (2.0 * read * m["kv_heads"] * (m["dim"] + m["vdim"]) + 4.0 * n * m["heads"] * m["dim"],
+                2.0 * _keys_seen(starts, counts, window) * m["heads"] * (m["dim"] + m["vdim"]))
+
+    def inner(r):
+        return r["heads"] * r["dim"]
+
+    def last(layer):
+        f = layer.get("mlp") or {}
+        if f.get("kind") == "dense":
+            return _product(n, W, f["ff"])
+        return (2.0 * n * W * (f["router"]["top"] + 1), 0.0) if f else None
+
+    return {
+        # (both norms of a layer come from one kernel: stream 4 + 4, up to three pending terms, two normed rows)
+        "norm1": lambda layer: (n * W * 18.0, 0.0),
+        "qkv": lambda layer: _product(n, att(layer)["heads"] * att(layer)["dim"] + att(layer)["kv_heads"] * (att(layer)["dim"] + att(layer)["vdim"]), W),
+        "q_rot": lambda layer: (4.0 * n * (att(layer)["heads"] * att(layer)["dim"] + att(layer)["kv_heads"] * (att(layer)["dim"] + att(layer)["vdim"])), 0.0),
+        "attn_out": attention,
+        "attn_turned_back": lambda layer: (4.0 * n * att(layer)["heads"] * att(layer)["vdim"], 0.0),
+        "attn_proj": lambda layer: _product(n, W, att(layer)["heads"] * att(layer)["vdim"]),
+        "shift_mixes": side(lambda r: (12.0 * n * W, 0.0)),
+        # (five products of the mixes and the decay's second small product)
+        "decay_in": side(lambda r: (2.0 * (4 * inner(r) * W + r["rank"] * (W + inner(r)) + n * (5 * W + 5 * inner(r) + 2 * r["rank"])),
+                                    2.0 * n * (4 * inner(r) * W + r["rank"] * (W + inner(r))))),
+        "decay_recurrence_out": side(lambda r: (2.0 * n * 4 * inner(r) + 4.0 * n * inner(r) + 8.0 * S * inner(r) * r["dim"], 0.0)),
+        "decay_normed": side(lambda r: (8.0 * n * inner(r), 0.0)),
+        "decay_proj": side(lambda r: _product(n, W, inner(r))),
+        "ffn_act": mlp("dense", lambda f: _product(n, 2 * f["ff"], W)),
+        "moe_ids": mlp("moe", lambda f: (4.0 * f["router"]["experts"] * W + 2.0 * n * W, 0.0)),
+        "moe_sorted": mlp("moe", lambda f: (12.0 * n * f["router"]["top"], 0.0)),
+        "moe_rows": mlp("moe", lambda f: (4.0 * n * f["router"]["top"] * W, 0.0)),
+        "moe_act": mlp("moe", lambda f: (2.0 * (touched(f) * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                         2.0 * n * f["router"]["top"] * f["expert"]["ff"] * W)),
+        "moe_expert_out": mlp("moe", lambda f: (2.0 * (touched(f) * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                                2.0 * n * f["router"]["top"] * f["expert"]["ff"] * W)),
+        "ffn_out": last,
+    }
+
+
+REVERAX_PHASES = {"norm1": "add (scale vectors) + two norms in groups", "qkv": "q/k/v product",
+                  "q_rot": lambda layer: "bias + rotation + cache write" if layer["type"] == "attention" else "bias + head norms + rotation of q, k and v + cache write",
+                  "attn_out": lambda layer: "attention with scores mixed over the heads" if layer["type"] == "attention" else "attention in a window, capped, with learned sinks",
+                  "attn_turned_back": "results turned back", "attn_proj": "attention output product",
+                  "shift_mixes": "token-shift mixes", "decay_in": "products of the mixes (r, k, v, g, decay)",
+                  "decay_recurrence_out": "recurrence with a learned decay", "decay_normed": "norm a head + gate",
+                  "decay_proj": "linear attention's output product", "ffn_act": "gate/up product + activation",
+                  "moe_ids": "router (sigmoid scores)", "moe_sorted": "grouping by expert", "moe_rows": "rows into the experts' order, weighted",
+                  "moe_act": "experts' up products + squared relu", "moe_expert_out": "experts' down products"}
+
+
 def _product(n, rows, cols):
     """(bytes, flops) of [n, cols] . [rows, cols]^T in bfloat16."""
     return 2.0 * (rows * cols + n * cols + n * rows), 2.0 * n * rows * cols
@@ -753,31 +852,36 @@ def family_bench(a):
     """Decode (batch ``a.batch`` at context CONTEXT) and prefill (PREFILL_TOKENS tokens) of Resolorn layers beside Qwen3
     layers of equal width, depth, head size and feed-forward width, with every phase against its roofline."""
     import torch
-    from rust_mlx_b200.config import GugalornConfig, Qwen3Config, ResolornConfig, SosuvikConfig
+    from rust_mlx_b200.config import GugalornConfig, Qwen3Config, ResolornConfig, ReveraxConfig, SosuvikConfig
     from rust_mlx_b200.engine import Engine
     from rust_mlx_b200.engine.batch import SequenceInput
     pk = peaks()
-    gug, sos = a.family == "gugalorn", a.family == "sosuvik"
-    sizes = GUGALORN_SIZES if gug else SOSUVIK_SIZES if sos else FAMILY_SIZES
-    out = {"metric": f"{a.family.capitalize()} beside {'Resolorn and ' if sos else ''}Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
+    gug, sos, rev = a.family == "gugalorn", a.family == "sosuvik", a.family == "reverax"
+    sizes = GUGALORN_SIZES if gug else SOSUVIK_SIZES if sos else REVERAX_SIZES if rev else FAMILY_SIZES
+    out = {"metric": f"{a.family.capitalize()} beside {'Resolorn and ' if sos else 'Gugalorn and ' if rev else ''}Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "batch": a.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
            "peaks": pk, "sizes": {}}
     for size in (a.family_size.split(",") if a.family_size else sorted(sizes)):
         s = sizes[size]
         groups = max(1, a.family_layers // 4)
         same = FAMILY_SIZES[size] if sos else s        # (the Resolorn layers of the same name have the sizes Sosuvik lacks)
-        raw_r = gugalorn_shape(groups=groups, **s) if gug else sosuvik_shape(groups=groups, **s) if sos else resolorn_shape(groups=groups, **s)
+        raw_r = gugalorn_shape(groups=groups, **s) if gug else sosuvik_shape(groups=groups, **s) if sos else \
+            reverax_shape(groups=groups, **s) if rev else resolorn_shape(groups=groups, **s)
         raw_q = dict(QWEN3_8B, num_hidden_layers=4 * groups, hidden_size=s["width"], num_attention_heads=s["heads"],
-                     num_key_value_heads=s["kv_heads"] if gug or sos else max(1, s["heads"] // 4), head_dim=s["dim"],
+                     num_key_value_heads=s["kv_heads"] if gug or sos or rev else max(1, s["heads"] // 4), head_dim=s["dim"],
                      intermediate_size=same["ff"], vocab_size=s["vocab"], max_position_embeddings=2 * MAX_CONTEXT)
         result = {}
         mine = ("gugalorn", raw_r, GugalornConfig.from_dict(raw_r), gugalorn_costs, GUGALORN_PHASES) if gug else \
                ("sosuvik", raw_r, SosuvikConfig.from_dict(raw_r), sosuvik_costs, SOSUVIK_PHASES) if sos else \
+               ("reverax", raw_r, ReveraxConfig.from_dict(raw_r), reverax_costs, REVERAX_PHASES) if rev else \
                ("resolorn", raw_r, ResolornConfig.from_dict(raw_r), resolorn_costs, RESOLORN_PHASES)
         others = []
         if sos:
             raw_o = resolorn_shape(groups=groups, **same)
             others.append(("resolorn", raw_o, ResolornConfig.from_dict(raw_o), resolorn_costs, RESOLORN_PHASES))
+        if rev:
+            raw_o = gugalorn_shape(groups=groups, **GUGALORN_SIZES[size])
+            others.append(("gugalorn", raw_o, GugalornConfig.from_dict(raw_o), gugalorn_costs, GUGALORN_PHASES))
         others.append(("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES))
         for family, raw, cfg, costs_of, names in (mine, *others):
             cache_tokens = a.batch * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64) + 2 * PREFILL_TOKENS
@@ -791,6 +895,8 @@ def family_bench(a):
             pf_ms = time_prefill(engine, PREFILL_TOKENS)
             if family == "qwen3":
                 layer_of = lambda run: {}
+            elif family == "reverax":       # (every layer of the configuration is a run, also one that uses another's tensors)
+                layer_of = lambda run, raw=raw: raw["layers"][run]
             else:       # a run of the schedule is a layer, or (past the layers) a loop's entry
                 layer_of = lambda run, raw=raw, calls=engine._calls: (raw["layers"][calls[run][0].layer]
                                                                       if calls[run][0].layer < len(raw["layers"]) else {"type": "loop"})
@@ -853,7 +959,7 @@ def main():
     ap.add_argument("--continuous", action="store_true",
                     help="instead: 64 requests with prompts of 128..3072 random ids, 256 tokens each, through the "
                          "scheduler with chunked prefill of 512 (continuous batching); prints its own JSON line")
-    ap.add_argument("--family", default="", choices=["", "resolorn", "gugalorn", "sosuvik"],
+    ap.add_argument("--family", default="", choices=["", "resolorn", "gugalorn", "sosuvik", "reverax"],
                     help="instead: layers of this design at sizes of real models beside Qwen3 layers of equal width, depth, head "
                          "size and feed-forward width: decode and prefill tok/s and every phase against its roofline; prints its own "
                          "JSON line")

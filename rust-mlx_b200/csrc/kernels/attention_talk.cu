@@ -10,7 +10,9 @@
 // are added depends on the token's position (and the window) only: not on how a prompt was cut, on the batch, the page
 // size or which pages hold the keys.
 //
-// attention_talk_kernel is the arrangement on the FMA units (both dtypes; the 32-bit path).
+// attention_talk_kernel is the arrangement on the FMA units (both dtypes; the 32-bit path, and in bfloat16 the decoded tokens,
+// whose keys may be split over several blocks that a second kernel merges).  attention_talk_mma_kernel is the arrangement
+// on the tensor cores for bfloat16 steps with prompt portions.
 #include "common.cuh"
 
 namespace {
@@ -21,10 +23,10 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
                                       const float* __restrict__ talk, const int* __restrict__ positions,
                                       const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride,
                                       int page_size, T* __restrict__ out, int nq, int nkv, int hd, int dq, int dv, int window,
-                                      float scale, int* __restrict__ status) {
+                                      float scale, int* __restrict__ status, int splits, float* __restrict__ partial) {
     extern __shared__ float smem[];
     const int group = nq / nkv;
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, split = blockIdx.y;
     const int head = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = head / group;
     const int kstride = dq + 1;
@@ -46,7 +48,14 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
     float m = -INFINITY, l = 0.f;
     const int row = nkv * dq;
 
-    for (int b = lo / TKB; b <= pos / TKB; ++b) {
+    // with splits, this block takes a run of the token's key blocks and leaves (m, l, unnormalised sums) for the merge
+    int b_first = lo / TKB, b_last = pos / TKB;
+    if (splits > 1) {
+        const int per = (b_last - b_first + splits) / splits;
+        b_first += split * per;
+        b_last = min(b_last, b_first + per - 1);
+    }
+    for (int b = b_first; b <= b_last; ++b) {
         const int base = b * TKB;
         __syncthreads();
         for (int idx = threadIdx.x; idx < TKB * row; idx += blockDim.x) {
@@ -102,6 +111,16 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
             }
         }
     }
+    if (splits > 1) {
+        float* dst = partial + (((size_t)t * splits + split) * nq + head) * (dv + 2);
+        if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per_lane && d < dv) dst[2 + d] = acc[i];
+        }
+        return;
+    }
     const float inv_l = 1.f / l;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -109,32 +128,319 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
         if (i < per_lane && d < dv) out[((size_t)t * nq + head) * dv + d] = from_float<T>(acc[i] * inv_l);
     }
 }
+
+// The shares of a token's key splits added up: one warp a (token, head); partial [tokens, splits, heads, 2 + dv] holds each
+// split's maximum, sum of weights and unnormalised sums (a split without keys left m = -inf, l = 0).
+template <typename T>
+__global__ void attention_talk_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int n_items, int nq, int dv, int splits) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= n_items) return;
+    const int t = item / nq, head = item - t * nq;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, partial[(((size_t)t * splits + s) * nq + head) * (dv + 2)]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* p = partial + (((size_t)t * splits + s) * nq + head) * (dv + 2);
+        if (p[1] > 0.f) l += p[1] * expf(p[0] - m);
+    }
+    const float inv_l = 1.f / l;
+    for (int d = lane; d < dv; d += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* p = partial + (((size_t)t * splits + s) * nq + head) * (dv + 2);
+            if (p[1] > 0.f) acc = fmaf(p[2 + d], expf(p[0] - m), acc);
+        }
+        out[((size_t)t * nq + head) * dv + d] = from_float<T>(acc * inv_l);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The arrangement on the tensor cores (bfloat16): a block takes 16 neighbouring tokens of one sequence with all heads, one
+// warp a head, and walks the keys in tiles of 32 aligned to absolute positions.  For a tile every warp forms its head's raw
+// scores S_g = Q_g K^T by mma.sync (m16n8k16, float accumulators) and leaves them, scaled, in shared memory; after a
+// barrier it forms its own mixed scores from all heads' (a float multiply-add a head and score: the scores stay 32-bit),
+// runs the online softmax on its accumulator fragment and adds P V by mma.sync, V fetched by ldmatrix.trans.  K and V of
+// all key heads of the tile are fetched once a block, 16 bytes a thread and piece, through the block table.
+constexpr int MT = 16, MB = 32;    // tokens a block, keys a tile
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+    const float* __restrict__ talk, const int* __restrict__ positions, const int* __restrict__ q_start, int n_seqs,
+    const int* __restrict__ block_table, int table_stride, int page_size, __nv_bfloat16* __restrict__ out, int nq, int nkv, int dv,
+    int window, float scale, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char talk_smem[];
+    constexpr int KS = HD + 8;                  // a key row in shared memory (16 bytes of padding: rows fall on different banks)
+    constexpr int SB = MB + 4;                  // a row of scores
+    allow_dependents();
+    wait_for_prior_kernels();
+    // which (sequence, tile of 16 tokens) this block takes: tiles are counted through the sequences in their order
+    int tile = blockIdx.x, seq = 0, r0 = 0, r1 = 0;
+    for (; seq < n_seqs; ++seq) {
+        r0 = q_start[seq];
+        r1 = q_start[seq + 1];
+        const int tiles = (r1 - r0 + MT - 1) / MT;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (seq >= n_seqs) return;
+    r0 += tile * MT;
+    const int rows = min(MT, r1 - r0);
+    const int head = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int kvh = head / (nq / nkv);
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(talk_smem);                 // [MB][nkv][KS]
+    __nv_bfloat16* Vs = Ks + (size_t)MB * nkv * KS;                                  // [MB][nkv][KS]
+    float* Ss = reinterpret_cast<float*>(Vs + (size_t)MB * nkv * KS);                // [nq][MT][SB]
+    float* Ts = Ss + (size_t)nq * MT * SB;                                           // [nq][nq]
+    const int* table = block_table + (size_t)seq * table_stride;
+    const int pos0 = positions[r0], pos_last = pos0 + rows - 1;
+    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
+    for (int g = lane; g < nq; g += 32) Ts[head * nq + g] = talk[head * nq + g];
+
+    // this head's queries as A fragments: rows gid and gid + 8 of the tile, all of a head's numbers
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* qrow0 = q + ((size_t)(r0 + gid) * nq + head) * HD;
+        const __nv_bfloat16* qrow1 = q + ((size_t)(r0 + gid + 8) * nq + head) * HD;
+        const bool ok0 = gid < rows, ok1 = gid + 8 < rows;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            const int c = ks * 16 + 2 * tig;
+            qa[ks][0] = ok0 ? *reinterpret_cast<const uint32_t*>(qrow0 + c) : 0u;
+            qa[ks][1] = ok1 ? *reinterpret_cast<const uint32_t*>(qrow1 + c) : 0u;
+            qa[ks][2] = ok0 ? *reinterpret_cast<const uint32_t*>(qrow0 + c + 8) : 0u;
+            qa[ks][3] = ok1 ? *reinterpret_cast<const uint32_t*>(qrow1 + c + 8) : 0u;
+        }
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // of rows gid and gid + 8 (sums: this thread's share)
+    const int prow0 = pos0 + gid, prow1 = pos0 + gid + 8;
+    const int lrow0 = window > 0 ? max(0, prow0 - window + 1) : 0, lrow1 = window > 0 ? max(0, prow1 - window + 1) : 0;
+    constexpr int PIECES = HD / 8;              // 16-byte pieces of a key row
+
+    for (int b = lo0 / MB; b <= pos_last / MB; ++b) {
+        const int base = b * MB;
+        __syncthreads();                        // (whoever still reads the tile before)
+        for (int idx = threadIdx.x; idx < MB * nkv * PIECES; idx += blockDim.x) {
+            const int piece = idx % PIECES, kh = (idx / PIECES) % nkv, j = idx / (PIECES * nkv);
+            const int kp = base + j;
+            uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = kv;
+            if (kp >= lo0 && kp <= pos_last) {
+                const int page = table[kp / page_size];
+                if (page >= 0) {
+                    const size_t off = (((size_t)page * nkv + kh) * page_size + kp % page_size) * HD + piece * 8;
+                    kv = *reinterpret_cast<const uint4*>(k_pool + off);
+                    vv = *reinterpret_cast<const uint4*>(v_pool + off);
+                } else if (piece == 0 && kh == 0) {
+                    atomicExch(status, 2);      // a key that should be there has no page
+                }
+            }
+            *reinterpret_cast<uint4*>(Ks + ((size_t)j * nkv + kh) * KS + piece * 8) = kv;
+            *reinterpret_cast<uint4*>(Vs + ((size_t)j * nkv + kh) * KS + piece * 8) = vv;
+        }
+        __syncthreads();
+        // raw scores of this head, scaled, into shared memory
+#pragma unroll
+        for (int nt = 0; nt < MB / 8; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const __nv_bfloat16* krow = Ks + ((size_t)(nt * 8 + gid) * nkv + kvh) * KS + 2 * tig;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                mma_bf16(c, qa[ks], *reinterpret_cast<const uint32_t*>(krow + ks * 16), *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8));
+            float* srow = Ss + ((size_t)head * MT + gid) * SB + nt * 8 + 2 * tig;
+            *reinterpret_cast<float2*>(srow) = make_float2(c[0] * scale, c[1] * scale);
+            *reinterpret_cast<float2*>(srow + 8 * SB) = make_float2(c[2] * scale, c[3] * scale);
+        }
+        __syncthreads();
+        // this head's mixed scores, at its own fragment's places
+        float s[MB / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < MB / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int g = 0; g < nq; ++g) {
+            const float w = Ts[head * nq + g];
+            const float* srow = Ss + ((size_t)g * MT + gid) * SB + 2 * tig;
+#pragma unroll
+            for (int nt = 0; nt < MB / 8; ++nt) {
+                const float2 a = *reinterpret_cast<const float2*>(srow + nt * 8);
+                const float2 c = *reinterpret_cast<const float2*>(srow + 8 * SB + nt * 8);
+                s[nt][0] = fmaf(w, a.x, s[nt][0]);
+                s[nt][1] = fmaf(w, a.y, s[nt][1]);
+                s[nt][2] = fmaf(w, c.x, s[nt][2]);
+                s[nt][3] = fmaf(w, c.y, s[nt][3]);
+            }
+        }
+        // which keys each row reads, the rows' maxima, the weights
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < MB / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int kp = base + nt * 8 + 2 * tig + e;
+                if (!(kp >= lrow0 && kp <= prow0)) s[nt][e] = -INFINITY;
+                if (!(kp >= lrow1 && kp <= prow1)) s[nt][2 + e] = -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        // (a row that has seen no key yet keeps zeros: nothing to rescale, no weights)
+        const float corr0 = n0 == -INFINITY ? 1.f : __expf(m0 - n0), corr1 = n1 == -INFINITY ? 1.f : __expf(m1 - n1);
+        const float ref0 = n0 == -INFINITY ? 0.f : n0, ref1 = n1 == -INFINITY ? 0.f : n1;
+        m0 = n0;
+        m1 = n1;
+        l0 *= corr0;
+        l1 *= corr1;
+#pragma unroll
+        for (int nt = 0; nt < MB / 8; ++nt) {
+            s[nt][0] = __expf(s[nt][0] - ref0);
+            s[nt][1] = __expf(s[nt][1] - ref0);
+            s[nt][2] = __expf(s[nt][2] - ref1);
+            s[nt][3] = __expf(s[nt][3] - ref1);
+            l0 += s[nt][0] + s[nt][1];
+            l1 += s[nt][2] + s[nt][3];
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= corr0; o[i][1] *= corr0;
+            o[i][2] *= corr1; o[i][3] *= corr1;
+        }
+        // O += P V: the weights are the A fragments as they stand, V comes transposed out of shared memory
+#pragma unroll
+        for (int kt = 0; kt < MB / 16; ++kt) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+            const __nv_bfloat16* vrow = Vs + ((size_t)(kt * 16 + (lane & 15)) * nkv + kvh) * KS;
+#pragma unroll
+            for (int dt = 0; dt < HD / 8; ++dt) {
+                uint32_t b0, b1;
+                const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vrow + dt * 8);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(addr));
+                mma_bf16(o[dt], pa, b0, b1);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; ++dt) {
+        const int d = dt * 8 + 2 * tig;
+        if (d < dv) {       // (dv is even whenever it is below HD's padding: a pair is written whole or not at all, except the last odd one)
+            __nv_bfloat16* dst0 = out + ((size_t)(r0 + gid) * nq + head) * dv + d;
+            __nv_bfloat16* dst1 = out + ((size_t)(r0 + gid + 8) * nq + head) * dv + d;
+            if (gid < rows) {
+                dst0[0] = __float2bfloat16_rn(o[dt][0] * inv0);
+                if (d + 1 < dv) dst0[1] = __float2bfloat16_rn(o[dt][1] * inv0);
+            }
+            if (gid + 8 < rows) {
+                dst1[0] = __float2bfloat16_rn(o[dt][2] * inv1);
+                if (d + 1 < dv) dst1[1] = __float2bfloat16_rn(o[dt][3] * inv1);
+            }
+        }
+    }
+}
+
+template <int HD>
+int launch_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
+                    int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
+                    int window, float scale, int* status, size_t smem, cudaStream_t s) {
+    static bool raised[64] = {};
+    if (rmx_first_on_device(raised)) {
+        cudaError_t e = cudaFuncSetAttribute(attention_talk_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) RMX_FAIL("attention_talk_mma: shared memory refused: %s", cudaGetErrorString(e));
+    }
+    const int tiles = (n_tokens + MT - 1) / MT + n_seqs;      // (an upper bound: blocks beyond the step's tiles leave at once)
+    RMX_CHECK_LAUNCHED(launch_dependent(attention_talk_mma_kernel<HD>, dim3(tiles), dim3(nq * 32), smem, s, (const __nv_bfloat16*)q,
+                                        (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, talk, positions, q_start, n_seqs,
+                                        block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, dv, window, scale, status),
+                       "attention_talk_mma");
+    return 0;
+}
 }  // namespace
+
+static size_t talk_mma_smem(int nq, int nkv, int hd) {
+    return 2 * (size_t)MB * nkv * (hd + 8) * 2 + ((size_t)nq * MT * (MB + 4) + (size_t)nq * nq) * 4;
+}
+
+// Whether the tensor-core arrangement takes these sizes (bfloat16 only): heads of a multiple of 16 numbers up to 128, and room
+// in shared memory for a tile's keys and values of all key heads and all heads' scores.
+RMX_API int rmx_attention_talk_mma_supports(int nq, int nkv, int hd) {
+    return nq > 0 && nq <= 32 && nkv > 0 && nq % nkv == 0 && hd >= 16 && hd <= 128 && hd % 16 == 0 && talk_mma_smem(nq, nkv, hd) <= 220 * 1024;
+}
+
+// q [tokens, nq, hd], pools with heads of hd numbers, talk float [nq, nq], out [tokens, nq, dv] dense; q_start [n_seqs + 1].
+RMX_API int rmx_attention_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions,
+                                   const int* q_start, int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size,
+                                   void* out, int nq, int nkv, int hd, int dv, int window, float scale, int* status, void* stream) {
+    if (n_tokens == 0 || n_seqs == 0) return 0;
+    RMX_REQUIRE(rmx_attention_talk_mma_supports(nq, nkv, hd), "attention_talk_mma: %d heads over %d key heads of %d numbers are not taken", nq, nkv, hd);
+    RMX_REQUIRE(dv > 0 && dv <= hd && page_size > 0 && table_stride > 0 && window >= 0 && talk && q_start, "attention_talk_mma: bad arguments");
+    RMX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0, "attention_talk_mma: operands must be 16-byte aligned");
+    const size_t smem = talk_mma_smem(nq, nkv, hd);
+    cudaStream_t s = (cudaStream_t)stream;
+#define TALK_CASE(HD_)                                                                                                                       \
+    case HD_: return launch_talk_mma<HD_>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, \
+                                          out, nq, nkv, dv, window, scale, status, smem, s);
+    switch (hd) {
+        TALK_CASE(16) TALK_CASE(32) TALK_CASE(48) TALK_CASE(64) TALK_CASE(80) TALK_CASE(96) TALK_CASE(112) TALK_CASE(128)
+    }
+#undef TALK_CASE
+    RMX_FAIL("attention_talk_mma: head size %d", hd);
+}
 
 // q [tokens, nq, hd] (the first dq numbers of a head count), pools with heads of hd numbers (keys: the first dq, values: the
 // first dv), talk float [nq, nq], out [tokens, nq, dv] dense.
 RMX_API int rmx_attention_talk(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions,
                                const int* seq_index, const int* block_table, int table_stride, int page_size, void* out,
                                int n_tokens, int nq, int nkv, int hd, int dq, int dv, int window, float scale, int* status,
-                               int dtype, void* stream) {
+                               int splits, float* partial, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq <= 32, "attention_talk: %d query heads over %d kv heads (at most 32)", nq, nkv);
     RMX_REQUIRE(dq > 0 && dv > 0 && dq <= hd && dv <= hd && hd <= 512, "attention_talk: head sizes %d %d in %d", dq, dv, hd);
     RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0 && talk, "attention_talk: bad page geometry or no mixing matrix");
     const size_t smem = ((size_t)TKB * nkv * (dq + 1) + (size_t)nq * TKB + (size_t)nq * dq + (size_t)nq * nq) * sizeof(float);
     RMX_REQUIRE(smem <= 200 * 1024, "attention_talk: %d key heads of %d numbers need too much shared memory", nkv, dq);
+    RMX_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial), "attention_talk: %d splits need room for their shares", splits);
     cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tokens, splits);
+    const int merge_blocks = (n_tokens * nq + 3) / 4;
     if (dtype == RMX_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_talk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_talk_kernel<float><<<n_tokens, nq * 32, smem, s>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, talk,
-                                                                     positions, seq_index, block_table, table_stride, page_size,
-                                                                     (float*)out, nq, nkv, hd, dq, dv, window, scale, status);
+        attention_talk_kernel<float><<<grid, nq * 32, smem, s>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, talk,
+                                                                 positions, seq_index, block_table, table_stride, page_size,
+                                                                 (float*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial);
+        if (splits > 1) attention_talk_merge_kernel<float><<<merge_blocks, 128, 0, s>>>(partial, (float*)out, n_tokens * nq, nq, dv, splits);
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(attention_talk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_talk_kernel<__nv_bfloat16><<<n_tokens, nq * 32, smem, s>>>(
+        attention_talk_kernel<__nv_bfloat16><<<grid, nq * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, talk, positions, seq_index,
-            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, dq, dv, window, scale, status);
+            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial);
+        if (splits > 1)
+            attention_talk_merge_kernel<__nv_bfloat16><<<merge_blocks, 128, 0, s>>>(partial, (__nv_bfloat16*)out, n_tokens * nq, nq, dv, splits);
     } else {
         RMX_FAIL("attention_talk: unknown dtype %d", dtype);
     }

@@ -544,6 +544,48 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ x, const float* __r
     if (write_state && t == q_start[seq + 1] - 1) last[(size_t)slots[seq] * channels + c] = x[idx];
 }
 
+// bfloat16, eight channels a thread (16-byte accesses; channels a multiple of eight): the same numbers.
+__global__ void token_shift_mix8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mu, __nv_bfloat16* __restrict__ out,
+                                        __nv_bfloat16* __restrict__ last, int channels, int n_mix, const int* __restrict__ positions,
+                                        const int* __restrict__ seq_index, const int* __restrict__ slots, const int* __restrict__ q_start,
+                                        size_t total8, int write_state) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx8 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx8 >= total8) return;
+    const int per_row = channels >> 3;
+    const int t = (int)(idx8 / per_row), c = (int)(idx8 - (size_t)t * per_row) * 8;
+    const size_t idx = (size_t)t * channels + c;
+    const int seq = seq_index[t];
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + idx);
+    uint4 before = make_uint4(0u, 0u, 0u, 0u);
+    if (t > q_start[seq]) before = *reinterpret_cast<const uint4*>(x + idx - channels);
+    else if (positions[t] > 0) before = *reinterpret_cast<const uint4*>(last + (size_t)slots[seq] * channels + c);
+    const uint32_t cw[4] = {raw.x, raw.y, raw.z, raw.w}, pw[4] = {before.x, before.y, before.z, before.w};
+    float cur[8], d[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cw[j]));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw[j]));
+        cur[2 * j] = a.x; cur[2 * j + 1] = a.y;
+        d[2 * j] = b.x - a.x; d[2 * j + 1] = b.y - a.y;
+    }
+    const size_t total = total8 * 8;
+    for (int s = 0; s < n_mix; ++s) {
+        const float4 m0 = *reinterpret_cast<const float4*>(mu + (size_t)s * channels + c);
+        const float4 m1 = *reinterpret_cast<const float4*>(mu + (size_t)s * channels + c + 4);
+        const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 r = __floats2bfloat162_rn(fmaf(d[2 * j], m[2 * j], cur[2 * j]), fmaf(d[2 * j + 1], m[2 * j + 1], cur[2 * j + 1]));
+            packed[j] = *reinterpret_cast<uint32_t*>(&r);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)s * total + idx) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    if (write_state && t == q_start[seq + 1] - 1) *reinterpret_cast<uint4*>(last + (size_t)slots[seq] * channels + c) = raw;
+}
+
 template <typename T>
 __global__ void token_shift_state_kernel(const T* __restrict__ x, T* __restrict__ last, int channels, const int* __restrict__ slots,
                                          const int* __restrict__ q_start, int n_seqs) {
@@ -768,9 +810,14 @@ RMX_API int rmx_token_shift_mix(const void* x, const float* mu, void* out, void*
             RMX_CHECK_LAUNCHED(launch_dependent(token_shift_state_kernel<float>, sgrid, dim3(256), 0, s, (const float*)x, (float*)last, channels,
                                                 slots, q_start, n_seqs), "token_shift_state");
     } else if (dtype == RMX_BF16) {
-        RMX_CHECK_LAUNCHED(launch_dependent(token_shift_mix_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, mu,
-                                            (__nv_bfloat16*)out, (__nv_bfloat16*)last, channels, n_mix, positions, seq_index, slots, q_start,
-                                            total, single_tokens), "token_shift_mix");
+        if (channels % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)last & 15) == 0 && ((uintptr_t)mu & 15) == 0)
+            RMX_CHECK_LAUNCHED(launch_dependent(token_shift_mix8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, s,
+                                                (const __nv_bfloat16*)x, mu, (__nv_bfloat16*)out, (__nv_bfloat16*)last, channels, n_mix, positions,
+                                                seq_index, slots, q_start, total / 8, single_tokens), "token_shift_mix");
+        else
+            RMX_CHECK_LAUNCHED(launch_dependent(token_shift_mix_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, mu,
+                                                (__nv_bfloat16*)out, (__nv_bfloat16*)last, channels, n_mix, positions, seq_index, slots, q_start,
+                                                total, single_tokens), "token_shift_mix");
         if (!single_tokens)
             RMX_CHECK_LAUNCHED(launch_dependent(token_shift_state_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, s, (const __nv_bfloat16*)x,
                                                 (__nv_bfloat16*)last, channels, slots, q_start, n_seqs), "token_shift_state");

@@ -646,21 +646,53 @@ def unrotate_heads(o, cos_sin, interleaved, out, heads, dv, hd):
 
 
 def attention_talk_plain(q, k_pool, v_pool, talk, positions, seq_index, block_table, page_size, out, nq, nkv, hd, dq, dv, window,
-                         scale, status):
+                         scale, status, splits=1, workspace=None):
     """Attention whose scaled scores are mixed over the heads before the softmax, s'_h = sum_g talk[h, g] s_g, on the FMA
     units: q [tokens, nq * hd], pools with heads of ``hd`` numbers (keys: the first dq, values: the first dv), talk float32
-    [nq, nq], out [tokens, nq * dv]."""
+    [nq, nq], out [tokens, nq * dv].  ``splits`` > 1: a token's keys are shared out over that many blocks whose shares a second
+    kernel adds (the order of a row's sums then follows the split: not for the 32-bit path)."""
     lib = kernels_library()
     n = q.shape[0]
     if q.shape != (n, nq * hd) or out.shape != (n, nq * dv) or talk.shape != (nq, nq) or out.dtype != q.dtype:
         raise KernelError("attention_talk_plain: shapes do not fit")
+    partial = None
+    if splits > 1:
+        ws = workspace if workspace is not None else _own_workspace()
+        partial = ws.get("talk_partial", (n, splits, nq, dv + 2), torch.float32)
     check(lib.rmx_attention_talk(_ptr(q, name="q"), _ptr(k_pool, q.dtype, "k_pool"), _ptr(v_pool, q.dtype, "v_pool"),
                                  _ptr(talk, torch.float32, "talk"), _ptr(positions, torch.int32, "positions"),
                                  _ptr(seq_index, torch.int32, "seq_index"), _ptr(block_table, torch.int32, "block_table"),
                                  c_int(block_table.shape[1]), c_int(page_size), _ptr(out, name="out"), c_int(n), c_int(nq), c_int(nkv),
                                  c_int(hd), c_int(dq), c_int(dv), c_int(window), c_float(scale), _ptr(status, torch.int32, "status"),
-                                 c_int(dtype_code(q)), _stream()))
+                                 c_int(splits), _ptr(partial), c_int(dtype_code(q)), _stream()))
+    _launched(1 if splits == 1 else 2)
+
+
+def attention_talk_mma_supported(nq: int, nkv: int, hd: int) -> bool:
+    return bool(kernels_library().rmx_attention_talk_mma_supports(c_int(nq), c_int(nkv), c_int(hd)))
+
+
+def attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale):
+    """The same attention on the tensor cores (bfloat16; mma.sync): a block takes 16 tokens of a sequence with all heads."""
+    lib = kernels_library()
+    n = q.shape[0]
+    if q.shape != (n, nq * hd) or out.shape != (n, nq * dv) or talk.shape != (nq, nq) or q.dtype != torch.bfloat16 or out.dtype != q.dtype:
+        raise KernelError("attention_talk_mma: shapes or dtypes do not fit")
+    check(lib.rmx_attention_talk_mma(_ptr(q, name="q"), _ptr(k_pool, q.dtype, "k_pool"), _ptr(v_pool, q.dtype, "v_pool"),
+                                     _ptr(talk, torch.float32, "talk"), _ptr(batch.positions, torch.int32, "positions"),
+                                     _ptr(batch.q_start, torch.int32, "q_start"), c_int(batch.n_seqs), c_int(n),
+                                     _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+                                     _ptr(out, name="out"), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(window), c_float(scale),
+                                     _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched()
+
+
+def talk_splits(n_tokens: int, max_seq_len: int, window: int = 0) -> int:
+    """Into how many blocks a decoded token's keys are split by the mixed-score attention: about two blocks an SM in all, no
+    block with fewer than four key blocks of 32."""
+    span = min(max_seq_len, window) if window else max_seq_len
+    blocks = -(-max(span, 1) // 32)
+    return max(1, min(2 * _sm_count() // max(n_tokens, 1), blocks // 4, 64))
 
 
 def token_shift_mix(x, mu, out, last, batch, slots):
@@ -1278,9 +1310,17 @@ class Kernels:
 
     def attention_talk(self, q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dq, dv, window, scale,
                        workspace=None):
-        """Attention whose scores are mixed over the heads before the softmax, over one step's batch."""
+        """Attention whose scores are mixed over the heads before the softmax, over one step's batch: in bfloat16 steps with
+        prompt portions take the tensor-core kernel (where it is built for the sizes), steps of decoded tokens alone the FMA
+        kernel with the keys split over blocks; the 32-bit path takes the FMA kernel unsplit (a fixed order of every sum)."""
+        if q.dtype == torch.bfloat16 and getattr(batch, "max_q_len", 1) > 1 and attention_talk_mma_supported(nq, nkv, hd):
+            attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale)
+            return
+        splits = 1
+        if q.dtype == torch.bfloat16 and getattr(batch, "max_q_len", 1) == 1:
+            splits = talk_splits(q.shape[0], batch.max_seq_len, window)
         attention_talk_plain(q, k_pool, v_pool, talk, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                             dq, dv, window, scale, batch.status)
+                             dq, dv, window, scale, batch.status, splits, workspace)
 
     def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype, chunk: int = 0) -> int:
         """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:

@@ -291,7 +291,9 @@ class TalkingAttentionMixer(Mixer):
             raise ValueError("scores are mixed over at most 32 heads")
         self.prefix, self.width = prefix, int(width)
         self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
-        self.head_dim = max(self.dim, self.vdim)
+        # of the cache and of q as the kernels read it: the larger of the two sizes, padded with zeros to the next multiple of 16
+        # (what the tensor-core kernel takes)
+        self.head_dim = -(-max(self.dim, self.vdim) // 16) * 16
         self.position, self.scale = position, float(scale) * float(getattr(position, "score_scale", 1.0))
         self.bias, self.window = bool(bias), int(window)
         self.names = {k: f"{prefix}.{v}" for k, v in {**self.NAMES, **(names or {})}.items()}
@@ -302,6 +304,10 @@ class TalkingAttentionMixer(Mixer):
 
     def cache_spec(self):
         return CacheSpec("paged", kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def graph_key(self, shape):
+        # the one launch shape of a decode step that follows the lengths: into how many blocks the keys are split
+        return (self.ctx.ops.talk_splits(shape.n_seqs, shape.max_seq_len, self.window),)
 
     def param_specs(self):
         n, qd, kd, vd = self.names, self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim

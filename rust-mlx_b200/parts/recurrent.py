@@ -187,6 +187,8 @@ class DecayLinearMixer(Mixer):
         n = self.names
         self.mu = torch.stack([tensors.pop(n["mu"].format(s=s)) for s in self.MIXES]).contiguous()
         self.w = {s: tensors[n[s]].contiguous() for s in ("r", "k", "v", "g", "w1", "w2")}
+        # r, k, v and g have one shape and each its own input: in bfloat16 they are one batched product of the library
+        self.w_four = torch.stack([self.w[s] for s in ("r", "k", "v", "g")]).transpose(1, 2) if ctx.dtype == torch.bfloat16 else None
         self.w0, self.u = tensors[n["w0"]].contiguous(), tensors[n["u"]].contiguous()
         self.norm_w, self.w_out = tensors[n["norm"]].contiguous(), tensors[n["out"]].contiguous()
 
@@ -203,8 +205,11 @@ class DecayLinearMixer(Mixer):
         if tap is not None:
             tap("shift_mixes", mixes)
         proj = ws.get("decay_in", (5, n, inner), dt)       # r, k, v, g and the decay's raw numbers
-        for i, s in enumerate(("r", "k", "v", "g")):
-            ops.linear(mixes[i], self.w[s], proj[i], ws, batch.status)
+        if self.w_four is not None:
+            torch.bmm(mixes[:4], self.w_four, out=proj[:4])
+        else:       # (the 32-bit path: every product on the FMA units in ascending k)
+            for i, s in enumerate(("r", "k", "v", "g")):
+                ops.linear(mixes[i], self.w[s], proj[i], ws, batch.status)
         low = ws.get("decay_low", (n, self.rank), dt)
         ops.linear(mixes[4], self.w["w1"], low, ws, batch.status)
         ops.unary_act(low, low, "tanh")

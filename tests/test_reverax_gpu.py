@@ -187,11 +187,13 @@ def talking_rows(q, k, v, talk, qpos, window, scale):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq, nkv, hd, dq, dv, page, window", [(4, 2, 16, 16, 16, 16, 0), (6, 2, 16, 16, 8, 8, 0), (3, 3, 12, 8, 12, 4, 21), (8, 8, 48, 48, 48, 64, 0),
                                                               (1, 1, 20, 12, 20, 16, 0), (8, 4, 32, 32, 32, 32, 50), (16, 2, 64, 64, 64, 64, 0)])
-def test_attention_with_scores_mixed_over_the_heads(dtype, nq, nkv, hd, dq, dv, page, window):
-    """Portions of several sequences beside single decoded tokens; NaN in every slot of the pools that must not be read; the
+@pytest.mark.parametrize("portions", [True, False])
+def test_attention_with_scores_mixed_over_the_heads(dtype, nq, nkv, hd, dq, dv, page, window, portions):
+    """Portions of several sequences beside single decoded tokens (in bfloat16: the tensor-core kernel where it takes the head
+    size), or decoded tokens alone (in bfloat16: keys split over blocks and merged); NaN in every slot of the pools that must not be read; the
     mixing matrix far from the identity, so that a head's row depends on every other head's scores."""
     dt = DT[dtype]
-    lengths, new = [150, 37, 260, 1, 64], [150, 1, 45, 1, 1]
+    lengths, new = ([150, 37, 260, 1, 64], [150, 1, 45, 1, 1]) if portions else ([700, 37, 260, 1, 1500], [1, 1, 1, 1, 1])
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     batch = _Batch(lengths, new, status)
     k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, dt, seed=nq)
