@@ -605,7 +605,7 @@ def reverax_shape(width, heads, kv_heads, dim, rot, right_heads, right_dim, rank
 REVERAX_SIZES = {
     "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, right_heads=32, right_dim=64, rank=64, ff=8192, experts=32, top=4,
                expert_ff=1024, vocab=32768, window=1024),
-    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, rot=64, right_heads=64, right_dim=64, rank=64, ff=12288, experts=64, top=6,
+    "4k": dict(width=4096, heads=16, kv_heads=4, dim=128, rot=64, right_heads=64, right_dim=64, rank=64, ff=12288, experts=64, top=6,
                expert_ff=1408, vocab=65536, window=1024),
 }
 

@@ -18,6 +18,14 @@
 namespace {
 constexpr int TKB = 32;   // keys per block
 
+__device__ __forceinline__ void talk_load4(const float* p, float4& v) { v = *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void talk_load4(const __nv_bfloat16* p, float4& v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v = make_float4(a.x, a.y, b.x, b.y);
+}
+
 template <typename T>
 __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                       const float* __restrict__ talk, const int* __restrict__ positions,
@@ -58,19 +66,38 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
     for (int b = b_first; b <= b_last; ++b) {
         const int base = b * TKB;
         __syncthreads();
-        for (int idx = threadIdx.x; idx < TKB * row; idx += blockDim.x) {
-            const int j = idx / row, r = idx - j * row;
-            const int kh = r / dq, d = r - kh * dq;
-            const int kp = base + j;
-            float kv = 0.f;
-            if (kp >= lo && kp <= pos) {
-                const int page = table[kp / page_size];
-                if (page >= 0)
-                    kv = to_float(k_pool[(((size_t)page * nkv + kh) * page_size + kp % page_size) * hd + d]);
-                else if (r == 0)
-                    atomicExch(status, 2);  // a key that should be there has no page
+        if (((dq | hd) & 3) == 0) {        // four numbers a load
+            const int row4 = row >> 2, dq4 = dq >> 2;
+            for (int idx = threadIdx.x; idx < TKB * row4; idx += blockDim.x) {
+                const int j = idx / row4, r = idx - j * row4;
+                const int kh = r / dq4, d = (r - kh * dq4) * 4;
+                const int kp = base + j;
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kp >= lo && kp <= pos) {
+                    const int page = table[kp / page_size];
+                    if (page >= 0)
+                        talk_load4(k_pool + (((size_t)page * nkv + kh) * page_size + kp % page_size) * hd + d, kv);
+                    else if (r == 0)
+                        atomicExch(status, 2);  // a key that should be there has no page
+                }
+                float* dst = Ks + ((size_t)j * nkv + kh) * kstride + d;
+                dst[0] = kv.x; dst[1] = kv.y; dst[2] = kv.z; dst[3] = kv.w;
             }
-            Ks[((size_t)j * nkv + kh) * kstride + d] = kv;
+        } else {
+            for (int idx = threadIdx.x; idx < TKB * row; idx += blockDim.x) {
+                const int j = idx / row, r = idx - j * row;
+                const int kh = r / dq, d = r - kh * dq;
+                const int kp = base + j;
+                float kv = 0.f;
+                if (kp >= lo && kp <= pos) {
+                    const int page = table[kp / page_size];
+                    if (page >= 0)
+                        kv = to_float(k_pool[(((size_t)page * nkv + kh) * page_size + kp % page_size) * hd + d]);
+                    else if (r == 0)
+                        atomicExch(status, 2);  // a key that should be there has no page
+                }
+                Ks[((size_t)j * nkv + kh) * kstride + d] = kv;
+            }
         }
         __syncthreads();
         const int kp = base + lane;
@@ -99,15 +126,26 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
             const int page = table[kp / page_size];
             if (page >= 0) voff = (long long)((((size_t)page * nkv + kvh) * page_size + kp % page_size) * hd);
         }
-        for (int j = 0; j < TKB; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            const long long off = __shfl_sync(0xffffffffu, voff, j);
-            if (off < 0) continue;
-            const T* vrow = v_pool + off;
+        // eight keys' values are asked for before the first is used (the sums keep the keys' order).  Every lane takes part
+        // in the shuffles; only what follows them depends on the lane's column.
+        for (int j0 = 0; j0 < TKB; j0 += 8) {
+            float pj[8];
+            long long off[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                pj[j] = __shfl_sync(0xffffffffu, p, j0 + j);
+                off[j] = __shfl_sync(0xffffffffu, voff, j0 + j);
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int d = lane + 32 * i;
-                if (i < per_lane && d < dv) acc[i] = fmaf(pj, to_float(vrow[d]), acc[i]);
+                if (i < per_lane && d < dv) {
+                    float vv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) vv[j] = off[j] >= 0 ? to_float(v_pool[off[j] + d]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[i] = fmaf(pj[j], vv[j], acc[i]);
+                }
             }
         }
     }
@@ -175,12 +213,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
+__device__ __forceinline__ void talk_cp_async16(void* smem, const void* gmem, int bytes) {     // bytes 16, or 0: zeros are stored
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void talk_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void talk_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// NW: the most warps (heads) a block of this instance has; it bounds the registers a thread may take (16 heads: 128).
+// stages 2: the next tile's keys and values are copied (cp.async) while this tile is worked on; 1 where shared memory has
+// no room for two tiles.
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
     const float* __restrict__ talk, const int* __restrict__ positions, const int* __restrict__ q_start, int n_seqs,
     const int* __restrict__ block_table, int table_stride, int page_size, __nv_bfloat16* __restrict__ out, int nq, int nkv, int dv,
-    int window, float scale, int* __restrict__ status) {
+    int window, float scale, int* __restrict__ status, int stages) {
     extern __shared__ __align__(16) unsigned char talk_smem[];
     constexpr int KS = HD + 8;                  // a key row in shared memory (16 bytes of padding: rows fall on different banks)
     constexpr int SB = MB + 4;                  // a row of scores
@@ -200,9 +247,9 @@ __global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
     const int rows = min(MT, r1 - r0);
     const int head = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int kvh = head / (nq / nkv);
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(talk_smem);                 // [MB][nkv][KS]
-    __nv_bfloat16* Vs = Ks + (size_t)MB * nkv * KS;                                  // [MB][nkv][KS]
-    float* Ss = reinterpret_cast<float*>(Vs + (size_t)MB * nkv * KS);                // [nq][MT][SB]
+    const size_t tile_elems = (size_t)MB * nkv * KS;
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(talk_smem);                 // [stages][K, V][MB][nkv][KS]
+    float* Ss = reinterpret_cast<float*>(KV + 2 * tile_elems * stages);              // [nq][MT][SB]
     float* Ts = Ss + (size_t)nq * MT * SB;                                           // [nq][nq]
     const int* table = block_table + (size_t)seq * table_stride;
     const int pos0 = positions[r0], pos_last = pos0 + rows - 1;
@@ -232,27 +279,44 @@ __global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
     const int lrow0 = window > 0 ? max(0, prow0 - window + 1) : 0, lrow1 = window > 0 ? max(0, prow1 - window + 1) : 0;
     constexpr int PIECES = HD / 8;              // 16-byte pieces of a key row
 
-    for (int b = lo0 / MB; b <= pos_last / MB; ++b) {
-        const int base = b * MB;
-        __syncthreads();                        // (whoever still reads the tile before)
+    // the copies of key tile b into buffer `stage`: keys outside what the block's rows read, and holes, become zeros
+    auto fetch = [&](int b, int stage) {
+        __nv_bfloat16* kd = KV + 2 * tile_elems * stage;
+        __nv_bfloat16* vd = kd + tile_elems;
         for (int idx = threadIdx.x; idx < MB * nkv * PIECES; idx += blockDim.x) {
             const int piece = idx % PIECES, kh = (idx / PIECES) % nkv, j = idx / (PIECES * nkv);
-            const int kp = base + j;
-            uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = kv;
+            const int kp = b * MB + j;
+            size_t off = 0;
+            int bytes = 0;
             if (kp >= lo0 && kp <= pos_last) {
                 const int page = table[kp / page_size];
                 if (page >= 0) {
-                    const size_t off = (((size_t)page * nkv + kh) * page_size + kp % page_size) * HD + piece * 8;
-                    kv = *reinterpret_cast<const uint4*>(k_pool + off);
-                    vv = *reinterpret_cast<const uint4*>(v_pool + off);
+                    off = (((size_t)page * nkv + kh) * page_size + kp % page_size) * HD + piece * 8;
+                    bytes = 16;
                 } else if (piece == 0 && kh == 0) {
                     atomicExch(status, 2);      // a key that should be there has no page
                 }
             }
-            *reinterpret_cast<uint4*>(Ks + ((size_t)j * nkv + kh) * KS + piece * 8) = kv;
-            *reinterpret_cast<uint4*>(Vs + ((size_t)j * nkv + kh) * KS + piece * 8) = vv;
+            const size_t at = ((size_t)j * nkv + kh) * KS + piece * 8;
+            talk_cp_async16(kd + at, k_pool + off, bytes);
+            talk_cp_async16(vd + at, v_pool + off, bytes);
+        }
+        talk_cp_async_commit();
+    };
+    const int b_first = lo0 / MB, b_last = pos_last / MB;
+    fetch(b_first, 0);
+    for (int b = b_first; b <= b_last; ++b) {
+        const int base = b * MB;
+        const int stage = stages == 2 ? (b - b_first) & 1 : 0;
+        if (stages == 2 && b < b_last) {
+            fetch(b + 1, stage ^ 1);            // (its buffer was last read a tile ago: everyone has passed that tile's last barrier)
+            talk_cp_async_wait<1>();
+        } else {
+            talk_cp_async_wait<0>();
         }
         __syncthreads();
+        const __nv_bfloat16* Ks = KV + 2 * tile_elems * stage;
+        const __nv_bfloat16* Vs = Ks + tile_elems;
         // raw scores of this head, scaled, into shared memory
 #pragma unroll
         for (int nt = 0; nt < MB / 8; ++nt) {
@@ -339,6 +403,8 @@ __global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
                 mma_bf16(o[dt], pa, b0, b1);
             }
         }
+        __syncthreads();                        // (the scores and this tile's buffer are free again)
+        if (stages == 1 && b < b_last) fetch(b + 1, 0);
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -363,32 +429,46 @@ __global__ void __launch_bounds__(1024) attention_talk_mma_kernel(
     }
 }
 
-template <int HD>
-int launch_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
-                    int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
-                    int window, float scale, int* status, size_t smem, cudaStream_t s) {
+template <int HD, int NW>
+int launch_talk_mma_n(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
+                      int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
+                      int window, float scale, int* status, size_t smem, int stages, cudaStream_t s) {
     static bool raised[64] = {};
     if (rmx_first_on_device(raised)) {
-        cudaError_t e = cudaFuncSetAttribute(attention_talk_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attention_talk_mma_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) RMX_FAIL("attention_talk_mma: shared memory refused: %s", cudaGetErrorString(e));
     }
     const int tiles = (n_tokens + MT - 1) / MT + n_seqs;      // (an upper bound: blocks beyond the step's tiles leave at once)
-    RMX_CHECK_LAUNCHED(launch_dependent(attention_talk_mma_kernel<HD>, dim3(tiles), dim3(nq * 32), smem, s, (const __nv_bfloat16*)q,
+    RMX_CHECK_LAUNCHED(launch_dependent(attention_talk_mma_kernel<HD, NW>, dim3(tiles), dim3(nq * 32), smem, s, (const __nv_bfloat16*)q,
                                         (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, talk, positions, q_start, n_seqs,
-                                        block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, dv, window, scale, status),
+                                        block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, dv, window, scale, status, stages),
                        "attention_talk_mma");
     return 0;
 }
+
+template <int HD>
+int launch_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
+                    int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
+                    int window, float scale, int* status, size_t smem, int stages, cudaStream_t s) {
+    if (nq <= 8)
+        return launch_talk_mma_n<HD, 8>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
+                                        nq, nkv, dv, window, scale, status, smem, stages, s);
+    if (nq <= 16)
+        return launch_talk_mma_n<HD, 16>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
+                                         nq, nkv, dv, window, scale, status, smem, stages, s);
+    return launch_talk_mma_n<HD, 32>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
+                                     nq, nkv, dv, window, scale, status, smem, stages, s);
+}
 }  // namespace
 
-static size_t talk_mma_smem(int nq, int nkv, int hd) {
-    return 2 * (size_t)MB * nkv * (hd + 8) * 2 + ((size_t)nq * MT * (MB + 4) + (size_t)nq * nq) * 4;
+static size_t talk_mma_smem(int nq, int nkv, int hd, int stages) {
+    return 2 * (size_t)stages * MB * nkv * (hd + 8) * 2 + ((size_t)nq * MT * (MB + 4) + (size_t)nq * nq) * 4;
 }
 
 // Whether the tensor-core arrangement takes these sizes (bfloat16 only): heads of a multiple of 16 numbers up to 128, and room
 // in shared memory for a tile's keys and values of all key heads and all heads' scores.
 RMX_API int rmx_attention_talk_mma_supports(int nq, int nkv, int hd) {
-    return nq > 0 && nq <= 32 && nkv > 0 && nq % nkv == 0 && hd >= 16 && hd <= 128 && hd % 16 == 0 && talk_mma_smem(nq, nkv, hd) <= 220 * 1024;
+    return nq > 0 && nq <= 32 && nkv > 0 && nq % nkv == 0 && hd >= 16 && hd <= 128 && hd % 16 == 0 && talk_mma_smem(nq, nkv, hd, 1) <= 220 * 1024;
 }
 
 // q [tokens, nq, hd], pools with heads of hd numbers, talk float [nq, nq], out [tokens, nq, dv] dense; q_start [n_seqs + 1].
@@ -399,11 +479,12 @@ RMX_API int rmx_attention_talk_mma(const void* q, const void* k_pool, const void
     RMX_REQUIRE(rmx_attention_talk_mma_supports(nq, nkv, hd), "attention_talk_mma: %d heads over %d key heads of %d numbers are not taken", nq, nkv, hd);
     RMX_REQUIRE(dv > 0 && dv <= hd && page_size > 0 && table_stride > 0 && window >= 0 && talk && q_start, "attention_talk_mma: bad arguments");
     RMX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0, "attention_talk_mma: operands must be 16-byte aligned");
-    const size_t smem = talk_mma_smem(nq, nkv, hd);
+    const int stages = talk_mma_smem(nq, nkv, hd, 2) <= 220 * 1024 ? 2 : 1;
+    const size_t smem = talk_mma_smem(nq, nkv, hd, stages);
     cudaStream_t s = (cudaStream_t)stream;
 #define TALK_CASE(HD_)                                                                                                                       \
     case HD_: return launch_talk_mma<HD_>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, \
-                                          out, nq, nkv, dv, window, scale, status, smem, s);
+                                          out, nq, nkv, dv, window, scale, status, smem, stages, s);
     switch (hd) {
         TALK_CASE(16) TALK_CASE(32) TALK_CASE(48) TALK_CASE(64) TALK_CASE(80) TALK_CASE(96) TALK_CASE(112) TALK_CASE(128)
     }
