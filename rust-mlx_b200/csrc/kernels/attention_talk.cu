@@ -198,8 +198,10 @@ __global__ void attention_talk_merge_kernel(const float* __restrict__ partial, T
 // The arrangement on the tensor cores (bfloat16): a block takes 16 neighbouring tokens of one sequence with all heads, one
 // warp a head, and walks the keys in tiles of 32 aligned to absolute positions.  For a tile every warp forms its head's raw
 // scores S_g = Q_g K^T by mma.sync (m16n8k16, float accumulators) and leaves them, scaled, in shared memory; after a
-// barrier it forms its own mixed scores from all heads' (a float multiply-add a head and score: the scores stay 32-bit),
-// runs the online softmax on its accumulator fragment and adds P V by mma.sync, V fetched by ldmatrix.trans.  K and V of
+// barrier the block's threads mix them in place, a thread a (token, key) pair with all its heads (a float multiply-add a
+// pair of heads and score: the scores stay 32-bit; a raw score is read once, not once a head); after another barrier
+// every warp takes its head's mixed scores back as its accumulator fragment, runs the online softmax on it and adds P V by
+// mma.sync, V fetched by ldmatrix.trans.  K and V of
 // all key heads of the tile are fetched once a block, 16 bytes a thread and piece, through the block table.
 constexpr int MT = 16, MB = 32;    // tokens a block, keys a tile
 
@@ -248,13 +250,14 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
     const int head = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int kvh = head / (nq / nkv);
     const size_t tile_elems = (size_t)MB * nkv * KS;
-    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(talk_smem);                 // [stages][K, V][MB][nkv][KS]
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(talk_smem);                 // [stages][K, V][nkv][MB][KS]
     float* Ss = reinterpret_cast<float*>(KV + 2 * tile_elems * stages);              // [nq][MT][SB]
     float* Ts = Ss + (size_t)nq * MT * SB;                                           // [nq][nq]
     const int* table = block_table + (size_t)seq * table_stride;
     const int pos0 = positions[r0], pos_last = pos0 + rows - 1;
     const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
-    for (int g = lane; g < nq; g += 32) Ts[head * nq + g] = talk[head * nq + g];
+    const int TS = (nq + 3) & ~3;               // a row of the mixing matrix in shared memory, padded with zeros
+    for (int g = lane; g < TS; g += 32) Ts[head * TS + g] = g < nq ? talk[head * nq + g] : 0.f;
 
     // this head's queries as A fragments: rows gid and gid + 8 of the tile, all of a head's numbers
     uint32_t qa[HD / 16][4];
@@ -297,7 +300,7 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
                     atomicExch(status, 2);      // a key that should be there has no page
                 }
             }
-            const size_t at = ((size_t)j * nkv + kh) * KS + piece * 8;
+            const size_t at = ((size_t)kh * MB + j) * KS + piece * 8;      // (a key head's rows are neighbours: rows fall on different banks)
             talk_cp_async16(kd + at, k_pool + off, bytes);
             talk_cp_async16(vd + at, v_pool + off, bytes);
         }
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
 #pragma unroll
         for (int nt = 0; nt < MB / 8; ++nt) {
             float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const __nv_bfloat16* krow = Ks + ((size_t)(nt * 8 + gid) * nkv + kvh) * KS + 2 * tig;
+            const __nv_bfloat16* krow = Ks + ((size_t)kvh * MB + nt * 8 + gid) * KS + 2 * tig;
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks)
                 mma_bf16(c, qa[ks], *reinterpret_cast<const uint32_t*>(krow + ks * 16), *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8));
@@ -330,21 +333,40 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
             *reinterpret_cast<float2*>(srow + 8 * SB) = make_float2(c[2] * scale, c[3] * scale);
         }
         __syncthreads();
+        // the scores are mixed in place, a thread a (token, key) pair of the tile: it takes the pair's raw scores of all heads
+        // (what every head's row needs is read once, not once a head), forms every head's mixed score in float, ascending g,
+        // and puts them back; nobody else touches the pair
+        for (int pair = threadIdx.x; pair < MT * MB; pair += blockDim.x) {
+            float* at = Ss + (size_t)(pair / MB) * SB + pair % MB;
+            float raw[NW];
+#pragma unroll
+            for (int g = 0; g < NW; ++g) raw[g] = g < nq ? at[(size_t)g * MT * SB] : 0.f;
+            for (int h = 0; h < nq; ++h) {
+                const float4* w4 = reinterpret_cast<const float4*>(Ts + h * TS);
+                float acc = 0.f;
+#pragma unroll
+                for (int g4 = 0; g4 < NW / 4; ++g4) {
+                    if (g4 * 4 < nq) {
+                        const float4 w = w4[g4];
+                        acc = fmaf(w.x, raw[4 * g4], acc);
+                        acc = fmaf(w.y, raw[4 * g4 + 1], acc);
+                        acc = fmaf(w.z, raw[4 * g4 + 2], acc);
+                        acc = fmaf(w.w, raw[4 * g4 + 3], acc);
+                    }
+                }
+                at[(size_t)h * MT * SB] = acc;
+            }
+        }
+        __syncthreads();
         // this head's mixed scores, at its own fragment's places
         float s[MB / 8][4];
-#pragma unroll
-        for (int nt = 0; nt < MB / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-        for (int g = 0; g < nq; ++g) {
-            const float w = Ts[head * nq + g];
-            const float* srow = Ss + ((size_t)g * MT + gid) * SB + 2 * tig;
+        {
+            const float* srow = Ss + ((size_t)head * MT + gid) * SB + 2 * tig;
 #pragma unroll
             for (int nt = 0; nt < MB / 8; ++nt) {
                 const float2 a = *reinterpret_cast<const float2*>(srow + nt * 8);
                 const float2 c = *reinterpret_cast<const float2*>(srow + 8 * SB + nt * 8);
-                s[nt][0] = fmaf(w, a.x, s[nt][0]);
-                s[nt][1] = fmaf(w, a.y, s[nt][1]);
-                s[nt][2] = fmaf(w, c.x, s[nt][2]);
-                s[nt][3] = fmaf(w, c.y, s[nt][3]);
+                s[nt][0] = a.x; s[nt][1] = a.y; s[nt][2] = c.x; s[nt][3] = c.y;
             }
         }
         // which keys each row reads, the rows' maxima, the weights
@@ -394,7 +416,7 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
             pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
             pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
             pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
-            const __nv_bfloat16* vrow = Vs + ((size_t)(kt * 16 + (lane & 15)) * nkv + kvh) * KS;
+            const __nv_bfloat16* vrow = Vs + ((size_t)kvh * MB + kt * 16 + (lane & 15)) * KS;
 #pragma unroll
             for (int dt = 0; dt < HD / 8; ++dt) {
                 uint32_t b0, b1;
@@ -462,7 +484,7 @@ int launch_talk_mma(const void* q, const void* k_pool, const void* v_pool, const
 }  // namespace
 
 static size_t talk_mma_smem(int nq, int nkv, int hd, int stages) {
-    return 2 * (size_t)stages * MB * nkv * (hd + 8) * 2 + ((size_t)nq * MT * (MB + 4) + (size_t)nq * nq) * 4;
+    return 2 * (size_t)stages * MB * nkv * (hd + 8) * 2 + ((size_t)nq * MT * (MB + 4) + (size_t)nq * ((nq + 3) & ~3)) * 4;
 }
 
 // Whether the tensor-core arrangement takes these sizes (bfloat16 only): heads of a multiple of 16 numbers up to 128, and room
