@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
     const float* __restrict__ talk, const int* __restrict__ positions, const int* __restrict__ q_start, int n_seqs,
     const int* __restrict__ block_table, int table_stride, int page_size, __nv_bfloat16* __restrict__ out, int nq, int nkv, int dv,
-    int window, float scale, int* __restrict__ status, int stages) {
+    int window, float scale, int* __restrict__ status, int stages, int splits, float* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char talk_smem[];
     constexpr int KS = HD + 8;                  // a key row in shared memory (16 bytes of padding: rows fall on different banks)
     constexpr int SB = MB + 4;                  // a row of scores
@@ -306,8 +306,14 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
         }
         talk_cp_async_commit();
     };
-    const int b_first = lo0 / MB, b_last = pos_last / MB;
-    fetch(b_first, 0);
+    // with splits (grid.y), this block takes a run of the tile's key tiles and leaves (m, l, unnormalised sums) for the merge
+    int b_first = lo0 / MB, b_last = pos_last / MB;
+    if (splits > 1) {
+        const int per = (b_last - b_first + splits) / splits;
+        b_first += blockIdx.y * per;
+        b_last = min(b_last, b_first + per - 1);
+    }
+    if (b_first <= b_last) fetch(b_first, 0);
     for (int b = b_first; b <= b_last; ++b) {
         const int base = b * MB;
         const int stage = stages == 2 ? (b - b_first) & 1 : 0;
@@ -432,6 +438,25 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (splits > 1) {
+        float* dst0 = partial + (((size_t)(r0 + gid) * splits + blockIdx.y) * nq + head) * (dv + 2);
+        float* dst1 = partial + (((size_t)(r0 + gid + 8) * splits + blockIdx.y) * nq + head) * (dv + 2);
+        if (tig == 0 && gid < rows) { dst0[0] = m0; dst0[1] = l0; }
+        if (tig == 0 && gid + 8 < rows) { dst1[0] = m1; dst1[1] = l1; }
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; ++dt) {
+            const int d = dt * 8 + 2 * tig;
+            if (gid < rows) {
+                if (d < dv) dst0[2 + d] = o[dt][0];
+                if (d + 1 < dv) dst0[3 + d] = o[dt][1];
+            }
+            if (gid + 8 < rows) {
+                if (d < dv) dst1[2 + d] = o[dt][2];
+                if (d + 1 < dv) dst1[3 + d] = o[dt][3];
+            }
+        }
+        return;
+    }
     const float inv0 = 1.f / l0, inv1 = 1.f / l1;
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt) {
@@ -454,16 +479,17 @@ __global__ void __launch_bounds__(NW * 32) attention_talk_mma_kernel(
 template <int HD, int NW>
 int launch_talk_mma_n(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
                       int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
-                      int window, float scale, int* status, size_t smem, int stages, cudaStream_t s) {
+                      int window, float scale, int* status, size_t smem, int stages, int splits, float* partial, cudaStream_t s) {
     static bool raised[64] = {};
     if (rmx_first_on_device(raised)) {
         cudaError_t e = cudaFuncSetAttribute(attention_talk_mma_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) RMX_FAIL("attention_talk_mma: shared memory refused: %s", cudaGetErrorString(e));
     }
     const int tiles = (n_tokens + MT - 1) / MT + n_seqs;      // (an upper bound: blocks beyond the step's tiles leave at once)
-    RMX_CHECK_LAUNCHED(launch_dependent(attention_talk_mma_kernel<HD, NW>, dim3(tiles), dim3(nq * 32), smem, s, (const __nv_bfloat16*)q,
+    RMX_CHECK_LAUNCHED(launch_dependent(attention_talk_mma_kernel<HD, NW>, dim3(tiles, splits), dim3(nq * 32), smem, s, (const __nv_bfloat16*)q,
                                         (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, talk, positions, q_start, n_seqs,
-                                        block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, dv, window, scale, status, stages),
+                                        block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, dv, window, scale, status, stages, splits,
+                                        partial),
                        "attention_talk_mma");
     return 0;
 }
@@ -471,15 +497,15 @@ int launch_talk_mma_n(const void* q, const void* k_pool, const void* v_pool, con
 template <int HD>
 int launch_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions, const int* q_start,
                     int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size, void* out, int nq, int nkv, int dv,
-                    int window, float scale, int* status, size_t smem, int stages, cudaStream_t s) {
+                    int window, float scale, int* status, size_t smem, int stages, int splits, float* partial, cudaStream_t s) {
     if (nq <= 8)
         return launch_talk_mma_n<HD, 8>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
-                                        nq, nkv, dv, window, scale, status, smem, stages, s);
+                                        nq, nkv, dv, window, scale, status, smem, stages, splits, partial, s);
     if (nq <= 16)
         return launch_talk_mma_n<HD, 16>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
-                                         nq, nkv, dv, window, scale, status, smem, stages, s);
+                                         nq, nkv, dv, window, scale, status, smem, stages, splits, partial, s);
     return launch_talk_mma_n<HD, 32>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, out,
-                                     nq, nkv, dv, window, scale, status, smem, stages, s);
+                                     nq, nkv, dv, window, scale, status, smem, stages, splits, partial, s);
 }
 }  // namespace
 
@@ -496,22 +522,31 @@ RMX_API int rmx_attention_talk_mma_supports(int nq, int nkv, int hd) {
 // q [tokens, nq, hd], pools with heads of hd numbers, talk float [nq, nq], out [tokens, nq, dv] dense; q_start [n_seqs + 1].
 RMX_API int rmx_attention_talk_mma(const void* q, const void* k_pool, const void* v_pool, const float* talk, const int* positions,
                                    const int* q_start, int n_seqs, int n_tokens, const int* block_table, int table_stride, int page_size,
-                                   void* out, int nq, int nkv, int hd, int dv, int window, float scale, int* status, void* stream) {
+                                   void* out, int nq, int nkv, int hd, int dv, int window, float scale, int* status, int splits,
+                                   float* partial, void* stream) {
     if (n_tokens == 0 || n_seqs == 0) return 0;
     RMX_REQUIRE(rmx_attention_talk_mma_supports(nq, nkv, hd), "attention_talk_mma: %d heads over %d key heads of %d numbers are not taken", nq, nkv, hd);
     RMX_REQUIRE(dv > 0 && dv <= hd && page_size > 0 && table_stride > 0 && window >= 0 && talk && q_start, "attention_talk_mma: bad arguments");
     RMX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0, "attention_talk_mma: operands must be 16-byte aligned");
+    RMX_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial), "attention_talk_mma: %d splits need room for their shares", splits);
     const int stages = talk_mma_smem(nq, nkv, hd, 2) <= 220 * 1024 ? 2 : 1;
     const size_t smem = talk_mma_smem(nq, nkv, hd, stages);
     cudaStream_t s = (cudaStream_t)stream;
-#define TALK_CASE(HD_)                                                                                                                       \
-    case HD_: return launch_talk_mma<HD_>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, \
-                                          out, nq, nkv, dv, window, scale, status, smem, stages, s);
+    int rc = -2;
+#define TALK_CASE(HD_)                                                                                                                     \
+    case HD_: rc = launch_talk_mma<HD_>(q, k_pool, v_pool, talk, positions, q_start, n_seqs, n_tokens, block_table, table_stride, page_size, \
+                                        out, nq, nkv, dv, window, scale, status, smem, stages, splits, partial, s); break;
     switch (hd) {
         TALK_CASE(16) TALK_CASE(32) TALK_CASE(48) TALK_CASE(64) TALK_CASE(80) TALK_CASE(96) TALK_CASE(112) TALK_CASE(128)
     }
 #undef TALK_CASE
-    RMX_FAIL("attention_talk_mma: head size %d", hd);
+    if (rc == -2) RMX_FAIL("attention_talk_mma: head size %d", hd);
+    if (rc != 0) return rc;
+    if (splits > 1) {
+        attention_talk_merge_kernel<__nv_bfloat16><<<(n_tokens * nq + 3) / 4, 128, 0, s>>>(partial, (__nv_bfloat16*)out, n_tokens * nq, nq, dv, splits);
+        RMX_CHECK_LAUNCH("attention_talk_merge");
+    }
+    return 0;
 }
 
 // q [tokens, nq, hd] (the first dq numbers of a head count), pools with heads of hd numbers (keys: the first dq, values: the

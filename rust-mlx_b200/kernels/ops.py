@@ -672,10 +672,16 @@ def attention_talk_mma_supported(nq: int, nkv: int, hd: int) -> bool:
     return bool(kernels_library().rmx_attention_talk_mma_supports(c_int(nq), c_int(nkv), c_int(hd)))
 
 
-def attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale):
-    """The same attention on the tensor cores (bfloat16; mma.sync): a block takes 16 tokens of a sequence with all heads."""
+def attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale, splits=1,
+                       workspace=None):
+    """The same attention on the tensor cores (bfloat16; mma.sync): a block takes 16 tokens of a sequence with all heads.
+    ``splits`` > 1: a tile's keys are shared out over that many blocks whose shares a second kernel adds."""
     lib = kernels_library()
     n = q.shape[0]
+    partial = None
+    if splits > 1:
+        ws = workspace if workspace is not None else _own_workspace()
+        partial = ws.get("talk_partial", (n, splits, nq, dv + 2), torch.float32)
     if q.shape != (n, nq * hd) or out.shape != (n, nq * dv) or talk.shape != (nq, nq) or q.dtype != torch.bfloat16 or out.dtype != q.dtype:
         raise KernelError("attention_talk_mma: shapes or dtypes do not fit")
     check(lib.rmx_attention_talk_mma(_ptr(q, name="q"), _ptr(k_pool, q.dtype, "k_pool"), _ptr(v_pool, q.dtype, "v_pool"),
@@ -683,16 +689,16 @@ def attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, o
                                      _ptr(batch.q_start, torch.int32, "q_start"), c_int(batch.n_seqs), c_int(n),
                                      _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
                                      _ptr(out, name="out"), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(window), c_float(scale),
-                                     _ptr(batch.status, torch.int32, "status"), _stream()))
-    _launched()
+                                     _ptr(batch.status, torch.int32, "status"), c_int(splits), _ptr(partial), _stream()))
+    _launched(1 if splits == 1 else 2)
 
 
 def talk_splits(n_tokens: int, max_seq_len: int, window: int = 0) -> int:
     """Into how many blocks a decoded token's keys are split by the mixed-score attention: about two blocks an SM in all, no
-    block with fewer than four key blocks of 32."""
+    block with fewer than two key blocks of 32."""
     span = min(max_seq_len, window) if window else max_seq_len
     blocks = -(-max(span, 1) // 32)
-    return max(1, min(2 * _sm_count() // max(n_tokens, 1), blocks // 4, 64))
+    return max(1, min(2 * _sm_count() // max(n_tokens, 1), blocks // 2, 64))
 
 
 def token_shift_mix(x, mu, out, last, batch, slots):
@@ -1311,14 +1317,15 @@ class Kernels:
     def attention_talk(self, q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dq, dv, window, scale,
                        workspace=None):
         """Attention whose scores are mixed over the heads before the softmax, over one step's batch: in bfloat16 steps with
-        prompt portions take the tensor-core kernel (where it is built for the sizes), steps of decoded tokens alone the FMA
-        kernel with the keys split over blocks; the 32-bit path takes the FMA kernel unsplit (a fixed order of every sum)."""
-        if q.dtype == torch.bfloat16 and getattr(batch, "max_q_len", 1) > 1 and attention_talk_mma_supported(nq, nkv, hd):
-            attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale)
-            return
+        prompt portions take the tensor-core kernel (where it is built for the sizes: otherwise the FMA kernel), and so do steps
+        of decoded tokens alone, with every sequence's keys split over several blocks whose shares a second kernel adds; the
+        32-bit path takes the FMA kernel unsplit (a fixed order of every sum)."""
         splits = 1
         if q.dtype == torch.bfloat16 and getattr(batch, "max_q_len", 1) == 1:
             splits = talk_splits(q.shape[0], batch.max_seq_len, window)
+        if q.dtype == torch.bfloat16 and attention_talk_mma_supported(nq, nkv, hd):
+            attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale, splits, workspace)
+            return
         attention_talk_plain(q, k_pool, v_pool, talk, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
                              dq, dv, window, scale, batch.status, splits, workspace)
 
