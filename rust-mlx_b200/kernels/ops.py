@@ -703,6 +703,51 @@ def talk_splits(n_tokens: int, max_seq_len: int, window: int = 0) -> int:
     return 1 << (most.bit_length() - 1)
 
 
+def token_shift_mix(x, mu, out, last, batch, slots):
+    """out[s] = x + (prev - x) * mu[s] for every mix s: ``x`` [tokens, channels], ``mu`` float32 [mixes, channels], ``out``
+    [mixes, tokens, channels]; prev is the row of the token before in the same sequence: of this step, or ``last``
+    [slots, channels] (what the sequence's last step left; written with the step's last rows), or zeros at position 0."""
+    lib = kernels_library()
+    n, channels = x.shape
+    mixes = mu.shape[0]
+    if mu.shape != (mixes, channels) or out.shape != (mixes, n, channels) or out.dtype != x.dtype or last.dtype != x.dtype \
+            or last.shape[1:] != (channels,):
+        raise KernelError("token_shift_mix: shapes or dtypes do not fit")
+    single = batch.max_q_len == 1
+    check(lib.rmx_token_shift_mix(_ptr(x, name="x"), _ptr(mu, torch.float32, "mu"), _ptr(out, name="out"), _ptr(last, name="last"),
+                                  c_int(channels), c_int(mixes), _ptr(batch.positions, torch.int32, "positions"),
+                                  _ptr(batch.seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
+                                  _ptr(batch.q_start, torch.int32, "q_start"), c_int(n), c_int(batch.n_seqs), c_int(1 if single else 0),
+                                  c_int(dtype_code(x)), _stream()))
+    _launched(1 if single else 2)
+
+
+def recurrence_decay(r, k, w, v, w0, u, state, out, batch, slots, heads, kdim, vdim, workspace=None, warps=None):
+    """Per head and channel a_t = exp(-exp(w_t + w0)); o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, then
+    S_t = diag(a_t) S_(t-1) + k_t v_t^T: ``r``, ``k``, ``w`` [tokens, heads * kdim] (columns of wider rows allowed), ``v``
+    [tokens, heads * vdim], ``w0`` and ``u`` float32 [heads * kdim], ``state`` float32 [slots, heads, vdim, kdim]
+    (transposed), ``out`` float32 [tokens, heads * vdim]."""
+    lib = kernels_library()
+    n = r.shape[0]
+    hk = heads * kdim
+    if r.shape != (n, hk) or k.shape != (n, hk) or w.shape != (n, hk) or v.shape != (n, heads * vdim) or out.shape != (n, heads * vdim) \
+            or state.shape[1:] != (heads, vdim, kdim) or w0.numel() != hk or u.numel() != hk or len({r.dtype, k.dtype, w.dtype, v.dtype}) != 1:
+        raise KernelError("recurrence_decay: shapes or dtypes do not fit")
+    kf, qf, af, _ = _recurrence_scratch(workspace, n, heads, heads, kdim, True)
+    ws = workspace if workspace is not None else _own_workspace()
+    bonus = ws.get("recurrence_bonus", (n, heads), torch.float32)
+    p0, l0 = _cols(r, "r")
+    p1, l1 = _cols(k, "k")
+    p2, l2 = _cols(w, "w")
+    p3, l3 = _cols(v, "v")
+    check(lib.rmx_decay_recurrence(_ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
+                                   _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
+                                   c_int(n), c_int(heads), c_int(kdim), c_int(vdim), p0, l0, p1, l1, p2, l2, p3, l3,
+                                   _ptr(w0, torch.float32, "w0"), _ptr(u, torch.float32, "u"), _ptr(af), _ptr(kf), _ptr(qf), _ptr(bonus),
+                                   c_int(warps or _recurrence_warps(batch, heads, vdim)), c_int(dtype_code(r)), _stream()))
+    _launched(2)
+
+
 def sample(logits, temperature, uniform, out, slots=None, last_tokens=None):
     """out[r] = greedy choice (temperature None or 0) or a draw from softmax(logits / temperature); with ``slots``
     and ``last_tokens`` the choice is also left at last_tokens[slots[r]] for the next step's embedding."""
