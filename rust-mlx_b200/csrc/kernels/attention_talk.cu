@@ -5,7 +5,7 @@
 //   p_h = softmax_j (s'_h[i, j]) over the keys that i reads;  o_h[i] = sum_j p_h[j] v_kv(h)[j]
 //
 // A query's row of scores therefore needs ALL heads' scores of the same (query, key) pair: a block takes a token with all
-// its heads, one warp a head.  Keys are visited in blocks of 32 aligned to absolute positions in ascending order with an
+// its heads, one warp a head.  Keys are visited in blocks of 32 (fewer for very wide key rows) aligned to absolute positions in ascending order with an
 // online softmax in float; a raw score is summed in ascending d, a mixed score in ascending g.  The order in which numbers
 // are added depends on the token's position (and the window) only: not on how a prompt was cut, on the batch, the page
 // size or which pages hold the keys.
@@ -16,7 +16,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int TKB = 32;   // keys per block
+constexpr int TKB_MOST = 32;   // keys per block, at most (fewer where shared memory has no room for 32 keys of all key heads)
 
 __device__ __forceinline__ void talk_load4(const float* p, float4& v) { v = *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void talk_load4(const __nv_bfloat16* p, float4& v) {
@@ -31,7 +31,7 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
                                       const float* __restrict__ talk, const int* __restrict__ positions,
                                       const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride,
                                       int page_size, T* __restrict__ out, int nq, int nkv, int hd, int dq, int dv, int window,
-                                      float scale, int* __restrict__ status, int splits, float* __restrict__ partial) {
+                                      float scale, int* __restrict__ status, int splits, float* __restrict__ partial, int TKB) {
     extern __shared__ float smem[];
     const int group = nq / nkv;
     const int t = blockIdx.x, split = blockIdx.y;
@@ -101,8 +101,8 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
         }
         __syncthreads();
         const int kp = base + lane;
-        const bool valid = kp >= lo && kp <= pos;
-        {
+        const bool valid = lane < TKB && kp >= lo && kp <= pos;
+        if (lane < TKB) {
             float s = 0.f;
             const float* qrow = Qs + head * dq;
             const float* krow = Ks + ((size_t)lane * nkv + kvh) * kstride;
@@ -111,7 +111,8 @@ __global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restri
         }
         __syncthreads();
         float s = 0.f;
-        for (int g = 0; g < nq; ++g) s = fmaf(Ts[head * nq + g], Ss[g * TKB + lane], s);
+        if (lane < TKB)
+            for (int g = 0; g < nq; ++g) s = fmaf(Ts[head * nq + g], Ss[g * TKB + lane], s);
         s = valid ? s : -INFINITY;
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -559,7 +560,12 @@ RMX_API int rmx_attention_talk(const void* q, const void* k_pool, const void* v_
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq <= 32, "attention_talk: %d query heads over %d kv heads (at most 32)", nq, nkv);
     RMX_REQUIRE(dq > 0 && dv > 0 && dq <= hd && dv <= hd && hd <= 512, "attention_talk: head sizes %d %d in %d", dq, dv, hd);
     RMX_REQUIRE(page_size > 0 && table_stride > 0 && window >= 0 && talk, "attention_talk: bad page geometry or no mixing matrix");
-    const size_t smem = ((size_t)TKB * nkv * (dq + 1) + (size_t)nq * TKB + (size_t)nq * dq + (size_t)nq * nq) * sizeof(float);
+    // keys a block: 32, or fewer where 32 keys of all key heads have no room (what the sizes alone decide: the order of a
+    // row's sums follows them)
+    int TKB = TKB_MOST;
+    auto need = [&](int kb) { return ((size_t)kb * nkv * (dq + 1) + (size_t)nq * kb + (size_t)nq * dq + (size_t)nq * nq) * sizeof(float); };
+    while (TKB > 8 && need(TKB) > 200 * 1024) TKB /= 2;
+    const size_t smem = need(TKB);
     RMX_REQUIRE(smem <= 200 * 1024, "attention_talk: %d key heads of %d numbers need too much shared memory", nkv, dq);
     RMX_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || partial), "attention_talk: %d splits need room for their shares", splits);
     cudaStream_t s = (cudaStream_t)stream;
@@ -569,14 +575,14 @@ RMX_API int rmx_attention_talk(const void* q, const void* k_pool, const void* v_
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_talk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_talk_kernel<float><<<grid, nq * 32, smem, s>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, talk,
                                                                  positions, seq_index, block_table, table_stride, page_size,
-                                                                 (float*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial);
+                                                                 (float*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial, TKB);
         if (splits > 1) attention_talk_merge_kernel<float><<<merge_blocks, 128, 0, s>>>(partial, (float*)out, n_tokens * nq, nq, dv, splits);
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(attention_talk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_talk_kernel<__nv_bfloat16><<<grid, nq * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, talk, positions, seq_index,
-            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial);
+            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, dq, dv, window, scale, status, splits, partial, TKB);
         if (splits > 1)
             attention_talk_merge_kernel<__nv_bfloat16><<<merge_blocks, 128, 0, s>>>(partial, (__nv_bfloat16*)out, n_tokens * nq, nq, dv, splits);
     } else {

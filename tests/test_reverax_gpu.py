@@ -186,7 +186,8 @@ def talking_rows(q, k, v, talk, qpos, window, scale):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq, nkv, hd, dq, dv, page, window", [(4, 2, 16, 16, 16, 16, 0), (6, 2, 16, 16, 8, 8, 0), (3, 3, 12, 8, 12, 4, 21), (8, 8, 48, 48, 48, 64, 0),
-                                                              (1, 1, 20, 12, 20, 16, 0), (8, 4, 32, 32, 32, 32, 50), (16, 2, 64, 64, 64, 64, 0)])
+                                                              (1, 1, 20, 12, 20, 16, 0), (8, 4, 32, 32, 32, 32, 50), (16, 2, 64, 64, 64, 64, 0),
+                                                              (16, 16, 128, 128, 128, 64, 0)])      # (the last: key rows so wide that a block takes 16 keys at a time)
 @pytest.mark.parametrize("portions", [True, False])
 def test_attention_with_scores_mixed_over_the_heads(dtype, nq, nkv, hd, dq, dv, page, window, portions):
     """Portions of several sequences beside single decoded tokens (in bfloat16: the tensor-core kernel where it takes the head
