@@ -26,8 +26,9 @@ __device__ __forceinline__ void talk_load4(const __nv_bfloat16* p, float4& v) {
     v = make_float4(a.x, a.y, b.x, b.y);
 }
 
+// (a block has up to 32 warps, one a head: the registers of a thread are bounded for the largest block)
 template <typename T>
-__global__ void attention_talk_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+__global__ void __launch_bounds__(1024) attention_talk_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                       const float* __restrict__ talk, const int* __restrict__ positions,
                                       const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride,
                                       int page_size, T* __restrict__ out, int nq, int nkv, int hd, int dq, int dv, int window,

@@ -1325,9 +1325,19 @@ class Kernels:
         splits = 1
         if q.dtype == torch.bfloat16 and getattr(batch, "max_q_len", 1) == 1:
             splits = talk_splits(q.shape[0], batch.max_seq_len, window)
+        elif q.dtype == torch.bfloat16:
+            # prompt portions: a causal prompt's tiles of 16 tokens are unequal (the last one walks all keys), and fewer than two
+            # an SM leave SMs idle behind the heaviest: then every tile's keys go to up to four blocks (while their shares
+            # stay a small buffer)
+            tiles = -(-q.shape[0] // 16) + batch.n_seqs
+            splits = max(1, min(4, -(-2 * _sm_count() // tiles)))
+            if q.shape[0] * splits * nq * (dv + 2) * 4 > (64 << 20):
+                splits = 1
         if q.dtype == torch.bfloat16 and attention_talk_mma_supported(nq, nkv, hd):
             attention_talk_mma(q, k_pool, v_pool, talk, batch, block_table, page_size, out, nq, nkv, hd, dv, window, scale, splits, workspace)
             return
+        if getattr(batch, "max_q_len", 1) > 1:
+            splits = 1      # (the FMA kernel splits the keys of decoded tokens only)
         attention_talk_plain(q, k_pool, v_pool, talk, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
                              dq, dv, window, scale, batch.status, splits, workspace)
 

@@ -187,7 +187,8 @@ def talking_rows(q, k, v, talk, qpos, window, scale):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq, nkv, hd, dq, dv, page, window", [(4, 2, 16, 16, 16, 16, 0), (6, 2, 16, 16, 8, 8, 0), (3, 3, 12, 8, 12, 4, 21), (8, 8, 48, 48, 48, 64, 0),
                                                               (1, 1, 20, 12, 20, 16, 0), (8, 4, 32, 32, 32, 32, 50), (16, 2, 64, 64, 64, 64, 0),
-                                                              (16, 16, 128, 128, 128, 64, 0)])      # (the last: key rows so wide that a block takes 16 keys at a time)
+                                                              (16, 16, 128, 128, 128, 64, 0),       # (key rows so wide that a block takes 16 keys at a time)
+                                                              (24, 8, 16, 16, 16, 16, 0), (32, 32, 32, 32, 32, 32, 7)])
 @pytest.mark.parametrize("portions", [True, False])
 def test_attention_with_scores_mixed_over_the_heads(dtype, nq, nkv, hd, dq, dv, page, window, portions):
     """Portions of several sequences beside single decoded tokens (in bfloat16: the tensor-core kernel where it takes the head
@@ -210,6 +211,29 @@ def test_attention_with_scores_mixed_over_the_heads(dtype, nq, nkv, hd, dq, dv, 
         qpos = torch.arange(length - c, length)
         want = talking_rows(q[at:at + c, :, :dq], ks[s][..., :dq], vs[s][..., :dv], talk, qpos, window, 0.3)
         close(out[at:at + c].view(c, nq, dv), want, dtype, (s, length, c))
+        at += c
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+@pytest.mark.parametrize("nq, nkv, hd, dv, window", [(4, 2, 16, 16, 0), (16, 4, 64, 64, 0), (6, 3, 48, 40, 90), (8, 8, 128, 128, 0)])
+def test_tensor_core_mixed_score_attention_with_and_without_key_splits(nq, nkv, hd, dv, window, splits):
+    """The tensor-core kernel called as it is, with tiles of up to 16 tokens whose keys go to 1, 2, 3 or 5 blocks (more blocks than
+    some tiles have key tiles: their shares are empty)."""
+    dt, page = torch.bfloat16, 32
+    lengths, new = [150, 37, 260, 1, 64, 300], [150, 1, 45, 1, 17, 2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = _Batch(lengths, new, status)
+    k_pool, v_pool, table, ks, vs = paged_setup(lengths, nkv, hd, page, dt, seed=nq)
+    talk = torch.eye(nq) + 0.5 * rnd((nq, nq), 4)
+    n = sum(new)
+    q = rnd((n, nq, hd), 5).to(dt)
+    out = torch.full((n, nq * dv), float("nan"), dtype=dt, device=DEV)
+    ops().attention_talk_mma(q.view(n, nq * hd).to(DEV), k_pool, v_pool, talk.to(DEV), batch, table, page, out, nq, nkv, hd, dv, window, 0.3, splits)
+    assert status.item() == 0
+    at = 0
+    for s, (length, c) in enumerate(zip(lengths, new)):
+        want = talking_rows(q[at:at + c], ks[s], vs[s][..., :dv], talk, torch.arange(length - c, length), window, 0.3)
+        close(out[at:at + c].view(c, nq, dv), want, "bfloat16", (s, length, c))
         at += c
 
 
