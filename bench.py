@@ -593,13 +593,13 @@ def reverax_shape(width, heads, kv_heads, dim, rot, right_heads, right_dim, rank
     tensors again with caches of their own, mixed-score attention with experts."""
     moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 1e6, "dims": rot}}
-    side = {"left": dict(att, softcap=30.0, mask={"size": window}, rot={"base": 1e6, "dims": rot}),
-            "right": {"heads": right_heads, "dim": right_dim, "rank": rank}, "left_scale": 1.2, "right_scale": 1.1}
+    side = {"left": dict(att, softcap=50.0, mask={"size": window}, rot={"base": 1e6, "dims": rot}),
+            "right": {"heads": right_heads, "dim": right_dim, "rank": rank}, "left_scale": 1.0, "right_scale": 0.5}
     layers = []
     for g in range(groups):
         layers += [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": ff}}, {"type": "parallel", "mixer": side, "mlp": moe},
                    {"type": "parallel", "mixer": side, "mlp": moe, "weights_of": 4 * g + 1}, {"type": "attention", "mixer": att, "mlp": moe}]
-    return {"architecture": "Reverax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2}, "logit_scale": 2.0, "layers": layers}
+    return {"architecture": "Reverax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4}, "logit_scale": 0.5, "layers": layers}
 
 
 REVERAX_SIZES = {

@@ -69,9 +69,9 @@ R2 = model(300, 96, [layer(side(2, 2, 32, 32, rot(1e4, 32), 0, 0.0, 2, 24, 3), m
                      layer(_T2, moe(16, 1, 1)),
                      layer(_T2, moe(16, 1, 1), weights_of=1),
                      layer(side(3, 1, 8, 8, rot(50.0, 4), 1, 2.0, 6, 8, 2, 0.5, 2.0), dense(20))], eps=1e-6)
-R3 = model(352, 128, [layer(side(8, 2, 64, 64, rot(2e5, 32), 100, 30.0, 2, 64, 16, 1.2, 1.1), moe(128, 8, 2)),
+R3 = model(352, 128, [layer(side(8, 2, 64, 64, rot(2e5, 32), 100, 25.0, 2, 64, 12, 1.3, 0.9), moe(128, 8, 2)),
                       layer(talk(8, 4, 32, 32, rot(1e4, 0)), dense(256)),
-                      layer(side(4, 4, 32, 64, rot(1e4, 32), 70, 0.0, 4, 32, 8), None)], groups=2, logit_scale=2.0)
+                      layer(side(4, 4, 32, 64, rot(1e4, 32), 70, 0.0, 4, 32, 8), None)], groups=4, logit_scale=1.5)
 R4 = model(97, 90, [layer(side(1, 1, 10, 6, rot(77.0, 4), 2, 3.0, 1, 14, 1, 0.9, 1.4, scale=0.4), moe(12, 9, 3)),
                     layer(talk(1, 1, 12, 20, rot(300.0, 12)), moe(20, 2, 1)),
                     layer(side(2, 1, 6, 10, rot(900.0, 6), 17, 0.0, 5, 6, 7), dense(36))], eps=1e-4, groups=5, logit_scale=0.25)
